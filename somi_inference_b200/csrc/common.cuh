@@ -1,0 +1,68 @@
+// Shared helpers for the sm_100a kernels of this library.
+//
+// Every exported launcher is `extern "C"`, takes raw device pointers, sizes and
+// the stream, launches on that stream and returns the cudaError_t of the launch
+// as an int (0 = success).  Floating tensors come with a dtype code:
+// 0 = float32, 1 = bfloat16.  Sizes that a kernel cannot take are refused with
+// SOMI_ERR_UNSUPPORTED before anything is launched; never a wrong result.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SOMI_F32 0
+#define SOMI_BF16 1
+#define SOMI_ERR_UNSUPPORTED 10001   // outside every cudaError_t value in use
+
+#define SOMI_API extern "C" __attribute__((visibility("default")))
+
+namespace somi {
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) {
+    return __float2bfloat16_rn(x);
+}
+
+__device__ __forceinline__ float load_as_float(const void* p, int dtype, size_t i) {
+    return dtype == SOMI_F32 ? reinterpret_cast<const float*>(p)[i]
+                             : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block; every thread gets the result.  `scratch` holds >= 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    float r = scratch[32];
+    __syncthreads();
+    return r;
+}
+
+inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
+
+}  // namespace somi

@@ -1,0 +1,114 @@
+"""The engine: a model, its cache and the one step function.
+
+The reference runs a step as separate forward passes: one whole prompt per new
+sequence, then one batch of single tokens (somi_inference/core/continuous_batching.py:200-203,
+somi_inference/core/model_runner.py:24-60).  Here `Engine.step` takes any mixture
+of (request, its next tokens) and runs exactly those tokens as one batch against
+the cache that earlier steps left, returning float32 logits at the wanted places.
+"""
+
+from __future__ import annotations
+
+from typing import Sequence
+
+import torch
+
+from ..cache import CacheManager, OutOfPages
+from ..config import load_config
+from ..parts import BuildContext, Decoder, declared_tensors
+from ..weights import load_tensors
+from .batch import BatchBuilder, StepBatch, StepEntry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32,
+           "fp32": torch.float32, torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def resolve_dtype(dtype) -> torch.dtype:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}") from None
+
+
+class Engine:
+    def __init__(self, model_dir: str, *, dtype="bfloat16", page_size: int = 16,
+                 num_pages: int | None = None, max_tokens: int | None = None,
+                 max_requests: int = 16, device: str | torch.device = "cuda:0",
+                 ops=None) -> None:
+        """Load `model_dir` (config.json + safetensors) and lay out its cache.
+
+        The page pool holds `num_pages` pages per group, or enough for
+        `max_tokens` tokens (rounded up to whole pages) when that is given.
+        """
+        self.device = torch.device(device)
+        self.dtype = resolve_dtype(dtype)
+        if ops is None:
+            from ..ops import cuda_ops
+            ops = cuda_ops()
+        self.ops = ops
+        self.config = load_config(model_dir)
+        self.spec = self.config.to_model_spec()
+        declared = declared_tensors(self.spec)
+        optional = ()
+        if self.spec.head.params.get("tied"):
+            optional = (self.spec.head.params["names"]["weight"],)
+        tensors = load_tensors(model_dir, declared, optional=optional)
+        ctx = BuildContext(dtype=self.dtype, device=self.device, ops=ops)
+        with torch.inference_mode():
+            self.model = Decoder(self.spec, tensors, ctx)
+            needs, owners = self.model.cache_needs()
+            if num_pages is None:
+                if max_tokens is None:
+                    raise ValueError("give num_pages or max_tokens")
+                num_pages = -(-int(max_tokens) // page_size)
+            self.page_size = page_size
+            self.num_pages = int(num_pages)
+            self.cache = CacheManager(needs, owners, num_pages=self.num_pages,
+                                      page_size=page_size, max_requests=max_requests,
+                                      max_positions=self.spec.max_positions, dtype=self.dtype,
+                                      device=self.device)
+        self.builder = BatchBuilder(self.cache, device=self.device,
+                                    q_tile_sizes=ops.q_tile_sizes,
+                                    vocab_size=self.spec.vocab_size,
+                                    max_positions=self.spec.max_positions)
+        self.last_batch: StepBatch | None = None
+
+    # ------------------------------------------------------------------ step
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one batch; return float32 logits [wanted, vocab] in the entries' order.
+
+        New requests are registered on first sight.  If the pages for this step
+        cannot all be had, `OutOfPages` is raised and the cache is as before.
+        """
+        registered: list[object] = []
+        reserved: list[object] = []
+        try:
+            for e in entries:
+                if not self.cache.is_registered(e.request):
+                    self.cache.register(e.request)
+                    registered.append(e.request)
+                self.cache.reserve(e.request, len(e.tokens))
+                reserved.append(e.request)
+            batch, _ = self.builder.build(entries)
+        except Exception:
+            for r in reserved:
+                self.cache.cancel(r)
+            for r in registered:
+                self.cache.release(r)
+            raise
+        with torch.inference_mode():
+            logits = self.model.forward(batch, self.cache)
+        for e in entries:
+            self.cache.commit(e.request)
+        self.last_batch = batch
+        return logits
+
+    def end(self, request: object) -> None:
+        """The request is finished: everything it holds goes back to the pools."""
+        self.cache.release(request)
+
+    def has(self, request: object) -> bool:
+        return self.cache.is_registered(request)
+
+    def length(self, request: object) -> int:
+        return self.cache.length(request)

@@ -1,0 +1,148 @@
+"""The kernel table of the product path: thin ctypes wrappers over `csrc/`.
+
+Every method checks what its kernel cannot check (devices, dtypes, contiguity),
+launches on torch's current stream and raises if the launch failed.  There is no
+other implementation behind these calls: without a CUDA device or without the
+compiled library, construction fails.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import build as _build
+
+_F32, _BF16 = 0, 1
+ERR_UNSUPPORTED = 10001
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise TypeError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _check(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError("the kernels of this engine run on a CUDA device only; got a "
+                              f"{t.device} tensor")
+        if not t.is_contiguous():
+            raise KernelError("kernel arguments must be contiguous")
+
+
+class CudaOps:
+    name = "cuda"
+
+    def __init__(self) -> None:
+        if not torch.cuda.is_available():
+            raise KernelError("no CUDA device: this engine has no CPU path")
+        major, minor = torch.cuda.get_device_capability()
+        if major != 10:
+            raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}{minor}")
+        self.lib_path = _build.build()
+        self.lib = ctypes.CDLL(self.lib_path)
+        self.lib.somi_attention_generic_q_tile.restype = ctypes.c_int
+        self.generic_q_tile = int(self.lib.somi_attention_generic_q_tile())
+        self.q_tile_sizes = (self.generic_q_tile,)
+        self.launches = 0     # kernels of this library launched so far
+
+    # ------------------------------------------------------------------ util
+    @staticmethod
+    def _stream() -> ctypes.c_void_p:
+        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _done(self, rc: int, what: str) -> None:
+        self.launches += 1
+        if rc == ERR_UNSUPPORTED:
+            raise KernelError(f"{what}: these sizes are not supported by the kernel")
+        if rc != 0:
+            raise KernelError(f"{what}: CUDA error {rc}")
+
+    def check_attention_geometry(self, num_heads: int, num_kv_heads: int, head_dim: int) -> None:
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise KernelError(f"head_dim {head_dim} is not supported: the attention kernels take "
+                              "multiples of 16 from 16 to 256")
+        if num_kv_heads <= 0 or num_heads % num_kv_heads:
+            raise KernelError(f"{num_heads} query heads cannot be grouped over {num_kv_heads} "
+                              "key/value heads")
+
+    # --------------------------------------------------------------- kernels
+    def embed(self, ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+        _check(ids, table, out)
+        assert ids.dtype == torch.int32 and out.dtype == torch.float32
+        rc = self.lib.somi_embed(_ptr(ids), _ptr(table), _code(table), _ptr(out),
+                                 ctypes.c_int(ids.shape[0]), ctypes.c_int(table.shape[1]),
+                                 self._stream())
+        self._done(rc, "embed")
+
+    def add_rmsnorm(self, residual, delta, weight, eps, out, rows=None) -> None:
+        _check(residual, delta, weight, out, rows)
+        assert residual.dtype == torch.float32
+        H = residual.shape[1]
+        n_out = out.shape[0]
+        rc = self.lib.somi_add_rmsnorm(
+            _ptr(residual), _ptr(delta), _code(delta) if delta is not None else _F32,
+            _ptr(weight), _code(weight), ctypes.c_float(eps), _ptr(out), _code(out), _ptr(rows),
+            ctypes.c_int(n_out), ctypes.c_int(H), ctypes.c_int(0 if rows is not None else 1),
+            self._stream())
+        self._done(rc, "add_rmsnorm")
+
+    def rope_store(self, qkv, positions, inv_freq, nq, nkv, hd, rotary_dim, slot_map, kcache,
+                   vcache) -> None:
+        _check(qkv, positions, inv_freq, slot_map, kcache, vcache)
+        page_size = kcache.shape[2] if kcache is not None else 1
+        if kcache is not None and slot_map is not None:
+            assert kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype
+        rc = self.lib.somi_rope_store(
+            _ptr(qkv), _code(qkv), _ptr(positions), _ptr(inv_freq), ctypes.c_int(qkv.shape[0]),
+            ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(rotary_dim),
+            _ptr(slot_map), _ptr(kcache), _ptr(vcache), ctypes.c_int(page_size), self._stream())
+        self._done(rc, "rope_store")
+
+    def paged_attention(self, qkv, kcache, vcache, batch, group, nq, nkv, hd, scale, window,
+                        out) -> None:
+        _check(qkv, kcache, vcache, out, group.block_table)
+        assert kcache.dtype == qkv.dtype
+        tiles = batch.tiles[self.generic_q_tile]
+        rc = self.lib.somi_paged_attention_generic(
+            _ptr(qkv), _code(qkv), ctypes.c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache),
+            _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+            _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
+            ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(batch.num_prefill_tokens),
+            ctypes.c_int(batch.num_requests - batch.num_prefill_requests),
+            ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(kcache.shape[2]),
+            ctypes.c_float(scale), ctypes.c_int(int(window) if window else 0), _ptr(out),
+            self._stream())
+        self._done(rc, "paged_attention")
+
+    def silu_mul(self, gu: torch.Tensor, out: torch.Tensor) -> None:
+        _check(gu, out)
+        rc = self.lib.somi_silu_mul(_ptr(gu), _ptr(out), _code(gu), ctypes.c_longlong(gu.shape[0]),
+                                    ctypes.c_int(out.shape[1]), self._stream())
+        self._done(rc, "silu_mul")
+
+
+_OPS: CudaOps | None = None
+
+
+def cuda_ops() -> CudaOps:
+    """The process-wide kernel table (built and loaded at first use)."""
+    global _OPS
+    if _OPS is None:
+        _OPS = CudaOps()
+    return _OPS

@@ -1,0 +1,27 @@
+"""How a layer's parts are arranged around the residual stream.
+
+Pre-norm (somi_inference/models/qwen2.py:325-339):
+    x = x + mixer(norm1(x));  x = x + feed_forward(norm2(x)).
+The residual stream `x` is float32 and the sums are made in float32, inside the
+norm kernel: a block receives the previous block's output as `pending`, adds it
+while normalising, and returns its own feed-forward output as the next `pending`.
+"""
+
+from __future__ import annotations
+
+from .registry import ARRANGEMENTS
+
+
+@ARRANGEMENTS.register("pre_norm")
+class PreNormBlock:
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm) -> None:
+        self.mixer = mixer
+        self.feed_forward = feed_forward
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(self, residual, pending, batch, cache, owns_cache):
+        h = self.mixer_norm.forward(residual, pending)
+        a = self.mixer.forward(h, batch, cache, owns_cache)
+        h = self.feed_forward_norm.forward(residual, a)
+        return self.feed_forward.forward(h, batch)

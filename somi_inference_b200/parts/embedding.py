@@ -1,0 +1,52 @@
+"""Token embedding and the output head.
+
+Embedding: x = E[ids] (somi_inference/models/qwen2.py:360,382), written straight
+into the float32 residual stream.  Head: logits = h E^T when tied
+(somi_inference/models/qwen2_adapter.py:60-62), else h W_lm^T with the file's
+`lm_head.weight`; logits are produced in float32 for the wanted rows only.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, TensorDecl, names_of
+from .linear import project_to_float32
+from .registry import EMBEDDINGS, HEADS
+
+
+@EMBEDDINGS.register("token_embedding")
+class TokenEmbedding:
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        return [TensorDecl(names_of(params)["weight"],
+                           (int(params["vocab_size"]), int(params["hidden_size"])))]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        self.ctx = ctx
+        self.weight = tensors[names_of(params)["weight"]]
+        self.hidden = int(params["hidden_size"])
+
+    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+        out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32,
+                          device=token_ids.device)
+        self.ctx.ops.embed(token_ids, self.weight, out)
+        return out
+
+
+@HEADS.register("lm_head")
+class LMHead:
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        if params["tied"]:
+            return []
+        return [TensorDecl(names_of(params)["weight"],
+                           (int(params["vocab_size"]), int(params["hidden_size"])))]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        n = names_of(params)
+        self.ctx = ctx
+        self.weight = tensors[n["tied_to"] if params["tied"] else n["weight"]]
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return project_to_float32(h, self.weight)

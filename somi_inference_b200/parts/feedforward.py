@@ -1,0 +1,40 @@
+"""Dense gated feed-forward (SwiGLU).
+
+Formula (somi_inference/models/qwen2.py:209-229): gu = h W_gu^T with
+W_gu = cat(gate_proj, up_proj) on the output dimension
+(somi_inference/models/qwen2_adapter.py:182-189,244-248); gate, up = the two
+halves; y = (silu(gate) * up) W_down^T; silu(z) = z * sigmoid(z), in float32.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .base import BuildContext, TensorDecl, names_of
+from .linear import Linear
+from .registry import FEED_FORWARDS
+
+
+@FEED_FORWARDS.register("swiglu")
+class SwiGLU:
+    @staticmethod
+    def declare(params) -> list[TensorDecl]:
+        n = names_of(params)
+        hidden, inter = int(params["hidden_size"]), int(params["intermediate_size"])
+        return [TensorDecl(n["gate_weight"], (inter, hidden)),
+                TensorDecl(n["up_weight"], (inter, hidden)),
+                TensorDecl(n["down_weight"], (hidden, inter))]
+
+    def __init__(self, params, tensors, ctx: BuildContext) -> None:
+        n = names_of(params)
+        self.ctx = ctx
+        self.inter = int(params["intermediate_size"])
+        self.gate_up = Linear(torch.cat([tensors[n["gate_weight"]], tensors[n["up_weight"]]], 0)
+                              .contiguous())
+        self.down = Linear(tensors[n["down_weight"]])
+
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        gu = self.gate_up(x)
+        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+        self.ctx.ops.silu_mul(gu, act)
+        return self.down(act)
