@@ -12,7 +12,7 @@ import ctypes
 
 import torch
 
-from . import build as _build
+from .build import build as _build_library
 
 _F32, _BF16 = 0, 1
 ERR_UNSUPPORTED = 10001
@@ -54,7 +54,7 @@ class CudaOps:
         major, minor = torch.cuda.get_device_capability()
         if major != 10:
             raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}{minor}")
-        self.lib_path = _build.build()
+        self.lib_path = _build_library()
         self.lib = ctypes.CDLL(self.lib_path)
         self.lib.somi_attention_generic_q_tile.restype = ctypes.c_int
         self.generic_q_tile = int(self.lib.somi_attention_generic_q_tile())

@@ -1,0 +1,171 @@
+"""Each CUDA kernel alone against its plain reference (tests/plain/host_ops.py, on the CPU in
+float32), at sizes other than the engine's tiny models: widths that are no power of two, head
+sizes 16..256 in steps of 16, odd group counts, several page sizes, windows."""
+
+import pytest
+import torch
+
+from tests.gpu_util import attention_case, batch_to_cpu
+from tests.plain.host_ops import HostOps
+
+pytestmark = pytest.mark.gpu
+HOST = HostOps()
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from somi_inference_b200.ops import cuda_ops
+    return cuda_ops()
+
+
+def tol(dtype):
+    return dict(rtol=1e-5, atol=1e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("V,H,T", [(1000, 80, 7), (517, 896, 33), (3001, 3584, 5)])
+def test_embed(ops, dtype, V, H, T):
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(V, H, generator=g).to(dtype)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    ids[0], ids[-1] = 0, V - 1
+    out = torch.empty(T, H, dtype=torch.float32, device="cuda")
+    ops.embed(ids.cuda(), table.cuda(), out)
+    ref = torch.empty(T, H)
+    HOST.embed(ids, table, ref)
+    assert torch.equal(out.cpu(), ref)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("N,H", [(9, 80), (4, 896), (3, 3584), (2, 5120), (5, 8192)])
+def test_add_rmsnorm(ops, dtype, wdtype, N, H):
+    g = torch.Generator().manual_seed(2)
+    res = torch.randn(N, H, generator=g) * 3
+    delta = torch.randn(N, H, generator=g).to(dtype)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(wdtype)
+    eps = 3e-5
+    for use_delta in (True, False):
+        r_gpu = res.clone().cuda()
+        out = torch.empty(N, H, dtype=dtype, device="cuda")
+        ops.add_rmsnorm(r_gpu, delta.cuda() if use_delta else None, w.cuda(), eps, out)
+        r_ref = res.clone()
+        ref = torch.empty(N, H, dtype=dtype)
+        HOST.add_rmsnorm(r_ref, delta if use_delta else None, w, eps, ref)
+        torch.testing.assert_close(r_gpu.cpu(), r_ref, rtol=0, atol=0)
+        torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(dtype))
+    # selected rows: residual untouched, rows gathered
+    rows = torch.tensor([N - 1, 0, N // 2], dtype=torch.int32)
+    r_gpu = res.clone().cuda()
+    out = torch.empty(3, H, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(r_gpu, delta.cuda(), w.cuda(), eps, out, rows.cuda())
+    ref = torch.empty(3, H, dtype=dtype)
+    HOST.add_rmsnorm(res.clone(), delta, w, eps, ref, rows)
+    assert torch.equal(r_gpu.cpu(), res)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(3, 176), (17, 4864), (2, 18944)])
+def test_silu_mul(ops, dtype, T, I):
+    g = torch.Generator().manual_seed(3)
+    gu = (torch.randn(T, 2 * I, generator=g) * 4).to(dtype)
+    out = torch.empty(T, I, dtype=dtype, device="cuda")
+    ops.silu_mul(gu.cuda(), out)
+    ref = torch.empty(T, I, dtype=dtype)
+    HOST.silu_mul(gu, ref)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,rot,ps", [(4, 2, 16, 16, 16), (14, 2, 64, 64, 16),
+                                             (28, 4, 128, 128, 16), (3, 1, 48, 48, 8),
+                                             (6, 3, 80, 32, 32), (2, 2, 256, 256, 64),
+                                             (5, 5, 32, 0, 16)])
+def test_rope_store(ops, dtype, nq, nkv, hd, rot, ps):
+    g = torch.Generator().manual_seed(4)
+    T, pages = 37, 12
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd, generator=g).to(dtype)
+    positions = torch.randint(0, 30000, (T,), generator=g, dtype=torch.int32)
+    positions[0] = 0
+    theta = 1e6
+    inv_freq = (1.0 / (theta ** (torch.arange(0, max(rot, 2), 2) / max(rot, 2)))).float()
+    slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32)
+    kc = torch.zeros(pages, nkv, ps, hd, dtype=dtype)
+    vc = torch.zeros(pages, nkv, ps, hd, dtype=dtype)
+    q_gpu, kc_gpu, vc_gpu = qkv.clone().cuda(), kc.clone().cuda(), vc.clone().cuda()
+    ops.rope_store(q_gpu, positions.cuda(), inv_freq.cuda(), nq, nkv, hd, rot, slots.cuda(),
+                   kc_gpu, vc_gpu)
+    q_ref = qkv.clone()
+    HOST.rope_store(q_ref, positions, inv_freq, nq, nkv, hd, rot, slots, kc, vc)
+    # angles reach 3e4 rad: sin/cos of the device and of the host differ by float32 rounding of
+    # the reduced argument, a few 1e-7 absolute on values of size ~4
+    t = dict(rtol=1e-5, atol=2e-5) if dtype == torch.float32 else tol(dtype)
+    torch.testing.assert_close(q_gpu.cpu().float(), q_ref.float(), **t)
+    torch.testing.assert_close(kc_gpu.cpu().float(), kc.float(), **t)
+    assert torch.equal(vc_gpu.cpu(), vc)
+    # without a slot map nothing is stored
+    kc2 = torch.zeros_like(kc_gpu)
+    ops.rope_store(qkv.clone().cuda(), positions.cuda(), inv_freq.cuda(), nq, nkv, hd, rot, None,
+                   kc2, kc2)
+    assert kc2.abs().sum().item() == 0
+
+
+ATT_CASES = [
+    # nq nkv hd ps window requests(ctx, q)
+    (4, 2, 16, 16, None, [(0, 5), (0, 17), (0, 33)]),
+    (14, 2, 64, 16, None, [(0, 70), (100, 1), (37, 2), (15, 1), (64, 16)]),
+    (28, 4, 128, 16, None, [(300, 1), (0, 40), (255, 1), (256, 1), (1, 1)]),
+    (3, 1, 48, 8, None, [(9, 31), (0, 1), (8, 8)]),
+    (6, 3, 32, 16, 24, [(0, 70), (50, 1), (23, 1), (24, 1), (25, 3), (5, 30)]),
+    (5, 5, 80, 32, 7, [(40, 9), (6, 1), (7, 1)]),
+    (2, 1, 256, 64, None, [(100, 3), (63, 2)]),
+    (8, 1, 112, 4, 130, [(200, 20), (129, 1), (130, 1), (131, 1)]),
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("case", ATT_CASES, ids=[f"c{i}" for i in range(len(ATT_CASES))])
+def test_paged_attention(ops, dtype, case):
+    nq, nkv, hd, ps, window, reqs = case
+    mgr, batch, qkv, view, _ = attention_case(ops, nq=nq, nkv=nkv, hd=hd, page_size=ps,
+                                              window=window, requests=reqs, dtype=dtype)
+    out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=dtype, device="cuda")
+    ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
+                        hd ** -0.5, window, out)
+    ref = torch.empty(batch.num_tokens, nq * hd, dtype=dtype)
+    HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), batch_to_cpu(batch),
+                         batch_to_cpu(batch).groups[0], nq, nkv, hd, hd ** -0.5, window, ref)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [None, 50])
+def test_attention_far_key_and_window_edge(ops, dtype, window):
+    """One key is made to dominate: the output must be its value, or must not see it at all.
+
+    The dominating key is put (a) far back among hundreds, (b) in the first slot of a page,
+    (c) in the last slot of a page, (d) exactly on the window's edge (seen) and (e) one position
+    beyond it (hidden)."""
+    nq, nkv, hd, ps = 4, 2, 64, 16
+    ctx = 400
+    mgr, batch, qkv, view, _ = attention_case(ops, nq=nq, nkv=nkv, hd=hd, page_size=ps,
+                                              window=window, requests=[(ctx, 1)], dtype=dtype)
+    qpos = ctx
+    spots = [3, 16 * 7, 16 * 9 - 1] if window is None else [qpos - window + 1, qpos - window]
+    table = batch.groups[0].block_table[0].cpu()
+    q = qkv.view(1, nq + 2 * nkv, hd)
+    for spot in spots:
+        keys = view.keys.clone()
+        page, off = int(table[spot // ps]), spot % ps
+        for h in range(nkv):
+            keys[page, h, off] = (q[0, h * (nq // nkv)].float() * 20).to(dtype)
+        out = torch.empty(1, nq * hd, dtype=dtype, device="cuda")
+        ops.paged_attention(qkv, keys, view.values, batch, batch.groups[0], nq, nkv, hd,
+                            hd ** -0.5, window, out)
+        got = out.view(nq, hd)[0].float()
+        planted = view.values[page, 0, off].float()
+        seen = window is None or spot > qpos - window
+        close = torch.allclose(got, planted, rtol=2e-2, atol=2e-2)
+        assert close == seen, f"key at {spot}: seen={seen}, output equals its value: {close}"

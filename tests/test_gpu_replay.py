@@ -1,0 +1,89 @@
+"""The engine against the plain implementation under every way of cutting the work.
+
+Same requests: whole; most in one step and the last 32 tokens one by one; in portions of
+changing size down to two tokens; and mixed, up to four live requests with so few pages that
+they are used again.  In float32 and bfloat16, for three tiny configurations, in-process and
+through the bin/trace_run program.
+"""
+
+import os
+
+import pytest
+import torch
+
+from tests import replay
+from tests.plain import qwen2_plain as plain
+from tests.tiny import PAGE_SIZES, TINY, make_model, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+# Weights are drawn with a larger spread than 0.02 so that attention scores differ by several
+# units and a wrong key or a wrong mask moves the logits by far more than the tolerance.
+STD = 0.08
+LENGTHS = [5, 97, 40, 70, 33, 100, 64, 81]
+# float32: logits are of size 3-5; differences between orders of summation stay below 3e-5.
+# bfloat16: every activation that passes between kernels is rounded to 8 bits of mantissa
+# (2^-9 relative each); the bound is stated relative to the largest logit of the model, 2e-2
+# of it (about ten such roundings compounded).  It was measured first on whole prompts, where
+# no cache or batching is involved (worst 1.7e-2 of the largest logit), and is the same for
+# every way of cutting: a fault of the cache or the batch moves logits by the logits' own size.
+ATOL = {"float32": lambda scale: 3e-5, "bfloat16": lambda scale: 2e-2 * scale}
+MODES = {"whole": replay.whole, "last32": replay.last_one_by_one, "portions": replay.portions,
+         "mixed": replay.mixed}
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = str(tmp_path_factory.mktemp("models"))
+    out = {}
+    for name in TINY:
+        for dt in (torch.float32, torch.bfloat16):
+            d = make_model(name, root, dt, std=STD)
+            cfg, w = plain.load_folder(d)       # float32 arithmetic on the stored values
+            reqs = {f"r{i}": random_tokens(n, cfg["vocab_size"], 10 + i)
+                    for i, n in enumerate(LENGTHS)}
+            ref = {k: plain.logits(cfg, w, v) for k, v in reqs.items()}
+            scale = max(v.abs().max().item() for v in ref.values())
+            out[(name, dt)] = (d, cfg, reqs, ref, scale)
+    return out
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_replay_in_process(models, name, dtype, mode):
+    from somi_inference_b200.engine import Engine
+    d, cfg, reqs, ref, scale = models[(name, getattr(torch, dtype))]
+    steps, max_tokens = MODES[mode](reqs)
+    eng = Engine(d, dtype=dtype, page_size=PAGE_SIZES[name], max_tokens=max_tokens)
+    got = replay.run_steps(eng, steps)
+    assert len(got) >= sum(1 for _ in reqs)
+    replay.compare(got, ref, ATOL[dtype](scale), f"{name}/{dtype}/{mode}")
+    assert all(f == eng.num_pages for f in eng.cache.free_pages()), "pages were lost"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_replay_program(models, tmp_path, name, dtype):
+    d, cfg, reqs, ref, scale = models[(name, getattr(torch, dtype))]
+    for mode in ("mixed", "last32"):
+        sub = {k: reqs[k] for k in list(reqs)[:5]} if mode == "last32" else reqs
+        steps, max_tokens = MODES[mode](sub)
+        out_dir = str(tmp_path / mode)
+        got = replay.run_trace_program(d, dtype, steps, max_tokens, out_dir, cfg["vocab_size"])
+        replay.compare(got, ref, ATOL[dtype](scale), f"trace_run {name}/{dtype}/{mode}")
+
+
+def test_cut_independence_float32(models):
+    """The same position computed whole and token by token differs by rounding only."""
+    from somi_inference_b200.engine import Engine
+    d, cfg, reqs, ref, scale = models[("C", torch.float32)]
+    sub = {"r1": reqs["r1"]}
+    outs = []
+    for mode in ("whole", "last32", "portions"):
+        steps, mt = MODES[mode](sub)
+        eng = Engine(d, dtype="float32", page_size=16, max_tokens=mt)
+        outs.append(replay.run_steps(eng, steps))
+    for key in outs[0]:
+        for o in outs[1:]:
+            assert (outs[0][key] - o[key]).abs().max().item() < 1e-5
