@@ -12,3 +12,8 @@ _torch.backends.cudnn.allow_tf32 = False
 _torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
 __version__ = "0.1.0"
+
+from .engine import LLM, Engine, StepEntry  # noqa: E402
+from .sampling import SamplingParams  # noqa: E402
+
+__all__ = ["LLM", "Engine", "StepEntry", "SamplingParams"]

@@ -54,7 +54,7 @@ class Engine:
             optional = (self.spec.head.params["names"]["weight"],)
         tensors = load_tensors(model_dir, declared, optional=optional)
         ctx = BuildContext(dtype=self.dtype, device=self.device, ops=ops)
-        with torch.inference_mode():
+        with torch.no_grad():
             self.model = Decoder(self.spec, tensors, ctx)
             needs, owners = self.model.cache_needs()
             if num_pages is None:
@@ -82,6 +82,11 @@ class Engine:
         """
         registered: list[object] = []
         reserved: list[object] = []
+        ids = [e.request for e in entries]
+        if len(set(ids)) != len(ids):
+            raise ValueError("a request appears twice in one step")
+        if any(len(e.tokens) < 1 for e in entries):
+            raise ValueError("every entry of a step needs at least one token")
         try:
             for e in entries:
                 if not self.cache.is_registered(e.request):
@@ -96,10 +101,20 @@ class Engine:
             for r in registered:
                 self.cache.release(r)
             raise
-        with torch.inference_mode():
-            logits = self.model.forward(batch, self.cache)
+        logits = self._run(batch)
         for e in entries:
             self.cache.commit(e.request)
+        return logits
+
+    def run_reserved(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """As `step`, for a caller (the scheduler) that registered the requests and reserved
+        their pages itself and will commit afterwards."""
+        batch, _ = self.builder.build(entries)
+        return self._run(batch)
+
+    def _run(self, batch: StepBatch) -> torch.Tensor:
+        with torch.no_grad():
+            logits = self.model.forward(batch, self.cache)
         self.last_batch = batch
         return logits
 

@@ -1,0 +1,171 @@
+"""The Python entry point: `LLM(model, ...).generate(prompt, max_new_tokens=...)`.
+
+Names and meanings of the options follow the reference's `LLM`
+(somi_inference/entrypoints/llm.py:58-70,126-135): `num_blocks`, `block_size`,
+`max_concurrent`, `device`, `dtype`, and for `generate`: `max_new_tokens`,
+`temperature`, `top_k`, `top_p`, `repetition_penalty`.  The reference takes a
+hub model name and a text prompt and returns text; here `model` is a folder
+(config.json + safetensors), a prompt may be a list of token ids (returned:
+list of new token ids) or, when the folder holds tokenizer files, a string
+(returned: the new text only, as llm.py:164).  Its three backend selectors do
+not exist: there is one implementation.  The loop below is the reference's
+`ContinuousBatchingEngine.run` (somi_inference/core/continuous_batching.py:179-205)
+over one mixed batch per step instead of separate prefill and decode passes.
+"""
+
+from __future__ import annotations
+
+import os
+import random
+from collections import deque
+from typing import Iterator, Sequence
+
+import torch
+
+from ..sampling import Sampler, SamplingParams
+from .batch import StepEntry
+from .engine import Engine
+from .scheduler import Request, Scheduler
+
+DEFAULT_BLOCK_SIZE = 16        # somi_inference/entrypoints/llm.py:25
+DEFAULT_MAX_CONCURRENT = 16    # somi_inference/entrypoints/llm.py:26
+DEFAULT_NUM_BLOCKS = 256       # somi_inference/entrypoints/llm.py:62
+
+
+class LLM:
+    def __init__(self, model: str, *, num_blocks: int = DEFAULT_NUM_BLOCKS,
+                 block_size: int = DEFAULT_BLOCK_SIZE,
+                 max_concurrent: int = DEFAULT_MAX_CONCURRENT,
+                 device: torch.device | str | None = None, dtype="float32",
+                 max_num_batched_tokens: int = 2048, chunk_size: int = 512,
+                 policy: str = "preempt", eos_token_id: int | None = None, ops=None) -> None:
+        self.device = torch.device(device) if device is not None else torch.device("cuda:0")
+        self.engine = Engine(model, dtype=dtype, page_size=block_size, num_pages=num_blocks,
+                             max_requests=max_concurrent, device=self.device, ops=ops)
+        self.config = self.engine.config
+        if eos_token_id is None:
+            eos_token_id = getattr(self.config, "eos_token_id", None)
+        self.eos_token_id = eos_token_id
+        self.scheduler = Scheduler(self.engine.cache, max_concurrent=max_concurrent,
+                                   max_num_batched_tokens=max_num_batched_tokens,
+                                   chunk_size=chunk_size,
+                                   max_positions=self.engine.spec.max_positions,
+                                   eos_token_id=eos_token_id, policy=policy)
+        self.sampler = Sampler(self.engine.ops, self.device)
+        self._next_request_id = 0
+        self._tokenizer = None
+        self._model_dir = model
+        self.steps_run = 0
+        self.d2h_bytes_last = 0
+
+    # -------------------------------------------------------------- tokenizer
+    def _tok(self):
+        if self._tokenizer is None:
+            if not any(os.path.isfile(os.path.join(self._model_dir, f))
+                       for f in ("tokenizer.json", "tokenizer_config.json", "vocab.json")):
+                raise ValueError("this model folder holds no tokenizer: give prompts as token ids")
+            from transformers import AutoTokenizer   # tokenizer only; no model code is used
+            self._tokenizer = AutoTokenizer.from_pretrained(self._model_dir, local_files_only=True)
+        return self._tokenizer
+
+    # --------------------------------------------------------------- requests
+    def make_request(self, prompt_tokens: Sequence[int], *, max_new_tokens: int,
+                     sampling_params: SamplingParams | None = None,
+                     ignore_eos: bool = False) -> Request:
+        sp = sampling_params or SamplingParams()
+        seed = sp.seed if sp.seed is not None else random.getrandbits(63)
+        req = Request(self._next_request_id, list(prompt_tokens), max_new_tokens, sp,
+                      ignore_eos=ignore_eos, seed=int(seed))
+        self._next_request_id += 1
+        return req
+
+    # ------------------------------------------------------------------- loop
+    def step(self) -> list[Request]:
+        """One scheduling step and one model step; returns the requests that finished in it."""
+        batch = self.scheduler.schedule()
+        if not batch.items:
+            if self.scheduler.has_unfinished() and not batch.preempted:
+                raise RuntimeError("nothing can be scheduled: the cache is too small for the "
+                                   "request at the head of the queue")
+            return []
+        entries = []
+        samplers = []
+        for item in batch.items:
+            toks = item.request.all_tokens[item.start:item.start + item.num_tokens]
+            entries.append(StepEntry(item.request.request_id, toks,
+                                     [item.num_tokens - 1] if item.samples else []))
+            if item.samples:
+                samplers.append(item.request)
+        logits = self.engine.run_reserved(entries)
+        sampled: dict[int, int] = {}
+        if samplers:
+            ids = self.sampler.sample(
+                logits, [r.sampling_params for r in samplers],
+                [len(r.output_tokens) for r in samplers], [r.seed for r in samplers],
+                [r.all_tokens if r.sampling_params.repetition_penalty != 1.0 else ()
+                 for r in samplers])
+            host = ids.cpu()
+            self.d2h_bytes_last = host.numel() * host.element_size()
+            sampled = {r.request_id: int(t) for r, t in zip(samplers, host.tolist())}
+        self.steps_run += 1
+        return self.scheduler.update(batch, sampled)
+
+    def run(self, requests: Sequence[tuple[int, Request]]) -> list[Request]:
+        """Run until all `(arrival_step, request)` pairs are finished
+        (somi_inference/core/continuous_batching.py:179-205)."""
+        pending = deque(sorted(requests, key=lambda p: p[0]))
+        finished: list[Request] = []
+        step = 0
+        while pending or self.scheduler.has_unfinished():
+            while pending and pending[0][0] <= step:
+                self.scheduler.add_request(pending.popleft()[1])
+            finished.extend(self.step())
+            self.scheduler.drain_finished()
+            step += 1
+        return finished
+
+    # --------------------------------------------------------------- generate
+    def generate(self, prompt: str | Sequence[int], *, max_new_tokens: int,
+                 temperature: float = 1.0, top_k: int = -1, top_p: float = 1.0,
+                 repetition_penalty: float = 1.0, seed: int | None = None,
+                 ignore_eos: bool = False) -> str | list[int]:
+        """Generate for one prompt; return only what is new (text for text, ids for ids)."""
+        is_text = isinstance(prompt, str)
+        tokens = self._tok().encode(prompt, add_special_tokens=False) if is_text else list(prompt)
+        sp = SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p,
+                            repetition_penalty=repetition_penalty, seed=seed)
+        req = self.make_request(tokens, max_new_tokens=max_new_tokens, sampling_params=sp,
+                                ignore_eos=ignore_eos)
+        finished = self.run([(0, req)])
+        assert len(finished) == 1, "generate expects exactly one finished request"
+        out = finished[0].output_tokens
+        return self._tok().decode(out, skip_special_tokens=True) if is_text else out
+
+    def generate_many(self, prompts: Sequence[Sequence[int]], *, max_new_tokens: int,
+                      sampling_params: SamplingParams | Sequence[SamplingParams] | None = None,
+                      arrival_steps: Sequence[int] | None = None,
+                      ignore_eos: bool = False) -> list[list[int]]:
+        """Several token-id prompts through the continuous-batching loop; outputs in input order."""
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params or SamplingParams()] * len(prompts)
+        arrival_steps = arrival_steps or [0] * len(prompts)
+        reqs = [self.make_request(p, max_new_tokens=max_new_tokens, sampling_params=sp,
+                                  ignore_eos=ignore_eos)
+                for p, sp in zip(prompts, sampling_params)]
+        self.run(list(zip(arrival_steps, reqs)))
+        return [r.output_tokens for r in reqs]
+
+    def generate_stream(self, prompt: Sequence[int], *, max_new_tokens: int,
+                        **sampling) -> Iterator[int]:
+        """Yield new token ids one by one (the reference leaves streaming unimplemented,
+        somi_inference/entrypoints/llm.py:166-170)."""
+        sp = SamplingParams(**sampling)
+        req = self.make_request(list(prompt), max_new_tokens=max_new_tokens, sampling_params=sp)
+        self.scheduler.add_request(req)
+        sent = 0
+        while self.scheduler.has_unfinished():
+            self.step()
+            self.scheduler.drain_finished()
+            while sent < len(req.output_tokens):
+                yield req.output_tokens[sent]
+                sent += 1

@@ -1,0 +1,227 @@
+"""Continuous-batching scheduler: admission, prompt portions under a token budget, decode,
+finish, and what happens when pages run out.
+
+The reference's scheduler (somi_inference/core/continuous_batching.py:46-120) is
+first-come-first-served over three queues, admits a sequence only if its
+worst-case block count ceil((prompt + max_new - 1) / block_size) fits beside the
+reservations of everything running (:64-67, :92-104), runs whole prompts, and so
+never runs out of blocks; a request larger than the pool blocks the queue for
+ever (:97-98).  This scheduler keeps the three queues, the FCFS order with
+head-of-line blocking, the finish rule (EOS or max_new_tokens, EOS kept in the
+output: :150-158) and `max_concurrent`, and adds:
+
+* a token budget per step and prompt portions of at most `chunk_size` tokens,
+  scheduled beside the single decode tokens of running requests;
+* pages are taken per step for exactly the scheduled tokens.  Policy "preempt"
+  (default): when a running request cannot get a page, the most recently
+  admitted running request is preempted by recompute: its pages go back, it
+  returns to the front of the waiting queue, and its prompt plus the tokens it
+  has generated are computed again when it is readmitted.  Policy "reserve":
+  the reference's worst-case reservation at admission, under which pages cannot
+  run out;
+* a request that could never fit (pool or position limit) is refused by
+  `add_request` with a ValueError instead of blocking the queue.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from enum import Enum
+
+from ..cache import OutOfPages
+from ..sampling import SamplingParams
+
+
+class RequestStatus(Enum):
+    WAITING = "waiting"
+    RUNNING = "running"
+    FINISHED = "finished"
+
+
+@dataclass
+class Request:
+    request_id: int
+    prompt_tokens: list[int]
+    max_new_tokens: int
+    sampling_params: SamplingParams = field(default_factory=SamplingParams)
+    ignore_eos: bool = False
+    seed: int = 0
+    status: RequestStatus = RequestStatus.WAITING
+    output_tokens: list[int] = field(default_factory=list)
+    num_computed: int = 0          # tokens whose keys/values are in the cache
+    num_preemptions: int = 0
+    finish_reason: str | None = None
+
+    def __post_init__(self) -> None:
+        if self.max_new_tokens <= 0:
+            raise ValueError("max_new_tokens must be > 0")
+        if not self.prompt_tokens:
+            raise ValueError("a request needs at least one prompt token")
+
+    @property
+    def all_tokens(self) -> list[int]:
+        return self.prompt_tokens + self.output_tokens
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt_tokens) + len(self.output_tokens)
+
+
+@dataclass
+class ScheduledItem:
+    request: Request
+    start: int            # index of the first token of the portion in request.all_tokens
+    num_tokens: int
+    samples: bool         # the portion reaches the request's last known token
+
+
+@dataclass
+class ScheduledBatch:
+    items: list[ScheduledItem]
+    preempted: list[Request]
+    admitted: list[Request]
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(i.num_tokens for i in self.items)
+
+
+class Scheduler:
+    def __init__(self, cache, *, max_concurrent: int, max_num_batched_tokens: int,
+                 chunk_size: int, max_positions: int, eos_token_id: int | None = None,
+                 policy: str = "preempt") -> None:
+        if policy not in ("preempt", "reserve"):
+            raise ValueError("policy must be 'preempt' or 'reserve'")
+        if max_num_batched_tokens < 1 or chunk_size < 1 or max_concurrent < 1:
+            raise ValueError("max_concurrent, max_num_batched_tokens and chunk_size must be >= 1")
+        self.cache = cache
+        self.max_concurrent = max_concurrent
+        self.max_num_batched_tokens = max_num_batched_tokens
+        self.chunk_size = chunk_size
+        self.max_positions = max_positions
+        self.eos_token_id = eos_token_id
+        self.policy = policy
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self.finished: list[Request] = []
+
+    # --------------------------------------------------------------- requests
+    def _pages_for(self, n_tokens: int) -> int:
+        return -(-n_tokens // self.cache.page_size)
+
+    def _worst_case_pages(self, req: Request) -> int:
+        """ceil((prompt + max_new - 1) / page_size), as continuous_batching.py:64-67."""
+        return self._pages_for(len(req.prompt_tokens) + req.max_new_tokens - 1)
+
+    def add_request(self, req: Request) -> None:
+        most = len(req.prompt_tokens) + req.max_new_tokens - 1
+        if most > self.max_positions:
+            raise ValueError(f"request {req.request_id}: prompt + max_new_tokens - 1 = {most} "
+                             f"exceeds the model's {self.max_positions} positions")
+        pool = min(g.pool.num_pages for g in self.cache.groups) if self.cache.groups else None
+        if pool is not None and self._worst_case_pages(req) > pool:
+            raise ValueError(f"request {req.request_id} needs {self._worst_case_pages(req)} pages "
+                             f"at its longest; the cache has {pool}")
+        req.status = RequestStatus.WAITING
+        self.waiting.append(req)
+
+    def has_unfinished(self) -> bool:
+        return bool(self.waiting) or bool(self.running)
+
+    def drain_finished(self) -> list[Request]:
+        done, self.finished = self.finished, []
+        return done
+
+    # --------------------------------------------------------------- schedule
+    def _preempt(self, victim: Request, items: list[ScheduledItem],
+                 preempted: list[Request]) -> None:
+        self.cache.release(victim.request_id)
+        self.running.remove(victim)
+        items[:] = [i for i in items if i.request is not victim]
+        victim.status = RequestStatus.WAITING
+        victim.num_computed = 0
+        victim.num_preemptions += 1
+        self.waiting.appendleft(victim)
+        preempted.append(victim)
+
+    def schedule(self) -> ScheduledBatch:
+        budget = self.max_num_batched_tokens
+        items: list[ScheduledItem] = []
+        preempted: list[Request] = []
+        admitted: list[Request] = []
+
+        # 1. everything that is running continues: one decode token, or the next prompt portion
+        for req in list(self.running):
+            if req not in self.running:        # preempted while an earlier one was served
+                continue
+            if budget == 0:
+                break
+            left = req.num_tokens - req.num_computed
+            n = min(left, self.chunk_size, budget)
+            while True:
+                try:
+                    self.cache.reserve(req.request_id, n)
+                    break
+                except OutOfPages:
+                    victim = self.running[-1]
+                    self._preempt(victim, items, preempted)
+                    if victim is req:
+                        n = 0
+                        break
+            if n == 0:
+                continue
+            items.append(ScheduledItem(req, req.num_computed, n, req.num_computed + n == req.num_tokens))
+            budget -= n
+
+        # 2. admission, first come first served, head of the line blocks
+        reserved_worst = sum(self._worst_case_pages(r) for r in self.running)
+        while (self.waiting and len(self.running) < self.max_concurrent and budget > 0
+               and not preempted):
+            req = self.waiting[0]
+            n = min(req.num_tokens - req.num_computed, self.chunk_size, budget)
+            if self.policy == "reserve":
+                pool = min(g.pool.num_pages for g in self.cache.groups)
+                if reserved_worst + self._worst_case_pages(req) > pool:
+                    break
+            self.cache.register(req.request_id)
+            try:
+                self.cache.reserve(req.request_id, n)
+            except OutOfPages:
+                self.cache.release(req.request_id)
+                break
+            self.waiting.popleft()
+            req.status = RequestStatus.RUNNING
+            self.running.append(req)
+            admitted.append(req)
+            reserved_worst += self._worst_case_pages(req)
+            items.append(ScheduledItem(req, req.num_computed, n, req.num_computed + n == req.num_tokens))
+            budget -= n
+        return ScheduledBatch(items, preempted, admitted)
+
+    # ----------------------------------------------------------------- update
+    def update(self, batch: ScheduledBatch, sampled: dict[int, int]) -> list[Request]:
+        """After the step: advance, append sampled tokens, finish and free.
+
+        `sampled` maps request_id to the token sampled for every item with
+        `samples`.  Returns the requests that finished in this step.
+        """
+        done: list[Request] = []
+        for item in batch.items:
+            req = item.request
+            self.cache.commit(req.request_id)
+            req.num_computed += item.num_tokens
+            if not item.samples:
+                continue
+            token = int(sampled[req.request_id])
+            req.output_tokens.append(token)
+            hit_eos = (not req.ignore_eos and self.eos_token_id is not None
+                       and token == self.eos_token_id)
+            if hit_eos or len(req.output_tokens) >= req.max_new_tokens:
+                req.status = RequestStatus.FINISHED
+                req.finish_reason = "eos" if hit_eos else "length"
+                self.cache.release(req.request_id)
+                self.running.remove(req)
+                self.finished.append(req)
+                done.append(req)
+        return done

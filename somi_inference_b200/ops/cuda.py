@@ -136,6 +136,23 @@ class CudaOps:
                                     ctypes.c_int(out.shape[1]), self._stream())
         self._done(rc, "silu_mul")
 
+    def sample(self, logits, temperature, top_k, top_p, penalty, seed, counter, hist_off,
+               hist_tok, out) -> None:
+        """seed: int32 view of uint64 pairs [2 * rows]; counter: int32 view of uint32 [rows]."""
+        _check(logits, temperature, top_k, top_p, penalty, seed, counter, hist_off, hist_tok, out)
+        assert logits.dtype == torch.float32 and out.dtype == torch.int32
+        assert seed.data_ptr() % 8 == 0
+        rc = self.lib.somi_sample(_ptr(logits), ctypes.c_int(logits.shape[0]),
+                                  ctypes.c_int(logits.shape[1]), _ptr(temperature), _ptr(top_k),
+                                  _ptr(top_p), _ptr(penalty), _ptr(seed), _ptr(counter),
+                                  _ptr(hist_off), _ptr(hist_tok), _ptr(out), self._stream())
+        self._done(rc, "sample")
+
+    def uniform(self, seed: int, counter: int) -> float:
+        """The uniform number in [0, 1) that row (seed, counter) draws (host evaluation)."""
+        self.lib.somi_sample_uniform.restype = ctypes.c_float
+        return float(self.lib.somi_sample_uniform(ctypes.c_ulonglong(seed), ctypes.c_uint(counter)))
+
 
 _OPS: CudaOps | None = None
 

@@ -1,0 +1,6 @@
+"""Sampling: per-request parameters and the device sampler."""
+
+from .params import SamplingParams
+from .sampler import Sampler
+
+__all__ = ["SamplingParams", "Sampler"]

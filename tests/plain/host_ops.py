@@ -88,3 +88,15 @@ class HostOps:
         I = out.shape[1]
         g, u = gu[:, :I].float(), gu[:, I:].float()
         out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
+
+    def sample(self, logits, temperature, top_k, top_p, penalty, seed, counter, hist_off,
+               hist_tok, out) -> None:
+        from tests.plain.sampler_plain import sample_row
+        seeds = seed.cpu().numpy().view("uint64")
+        counters = counter.cpu().numpy().view("uint32")
+        for r in range(logits.shape[0]):
+            hist = hist_tok[int(hist_off[r]):int(hist_off[r + 1])].tolist()
+            tok, _, _ = sample_row(logits[r].cpu(), float(temperature[r]), int(top_k[r]),
+                                   float(top_p[r]), float(penalty[r]), hist, int(seeds[r]),
+                                   int(counters[r]))
+            out[r] = tok

@@ -35,6 +35,9 @@ def read_safetensors(path: str) -> dict[str, torch.Tensor]:
         if name == "__metadata__":
             continue
         b, t = e["data_offsets"]
+        if t == b:
+            out[name] = torch.empty(e["shape"], dtype=kinds[e["dtype"]])
+            continue
         out[name] = torch.frombuffer(bytearray(data[b:t]), dtype=kinds[e["dtype"]]).reshape(e["shape"]).clone()
     return out
 

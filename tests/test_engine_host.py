@@ -1,0 +1,122 @@
+"""The host side of the engine (batch layout, cache manager, order of runs, scheduler loop)
+checked on the CPU by handing the engine the test-only kernel table of tests/plain/host_ops.py.
+The product path never runs like this; the same checks run on the GPU with the CUDA kernels in
+tests/test_gpu_replay.py and tests/test_gpu_toy.py."""
+
+import pytest
+import torch
+
+from somi_inference_b200 import LLM, SamplingParams
+from somi_inference_b200.cache import OutOfPages
+from somi_inference_b200.config import register_architecture, unregister_architecture
+from somi_inference_b200.engine import Engine, StepEntry
+from tests import replay, toy_model
+from tests.plain import qwen2_plain as plain
+from tests.plain.host_ops import HostOps
+from tests.tiny import PAGE_SIZES, TINY, make_model, random_tokens
+from tests.toy_parts import register_toys, unregister_toys
+
+MODES = {"whole": replay.whole, "last32": replay.last_one_by_one, "portions": replay.portions,
+         "mixed": replay.mixed}
+
+
+@pytest.fixture(scope="module")
+def root(tmp_path_factory):
+    return str(tmp_path_factory.mktemp("host"))
+
+
+@pytest.mark.parametrize("mode", list(MODES))
+@pytest.mark.parametrize("name", list(TINY))
+def test_cuts_agree_with_plain(root, name, mode):
+    d = make_model(name, root, torch.float32, std=0.08)
+    cfg, w = plain.load_folder(d)
+    reqs = {f"r{i}": random_tokens(n, cfg["vocab_size"], 10 + i)
+            for i, n in enumerate([5, 97, 40, 70, 33, 64])}
+    ref = {k: plain.logits(cfg, w, v) for k, v in reqs.items()}
+    steps, max_tokens = MODES[mode](reqs)
+    eng = Engine(d, dtype="float32", page_size=PAGE_SIZES[name], max_tokens=max_tokens,
+                 device="cpu", ops=HostOps())
+    got = replay.run_steps(eng, steps)
+    replay.compare(got, ref, 3e-5, f"{name}/{mode}")
+    assert all(f == eng.num_pages for f in eng.cache.free_pages())
+
+
+def test_out_of_pages_leaves_the_cache_as_it_was(root):
+    d = make_model("A", root, torch.float32, std=0.08)
+    eng = Engine(d, dtype="float32", page_size=16, num_pages=4, device="cpu", ops=HostOps())
+    eng.step([StepEntry("a", list(range(40)), [39])])
+    free = eng.cache.free_pages()
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry("a", [1], [0]), StepEntry("b", list(range(30)), [29])])
+    assert eng.cache.free_pages() == free and not eng.has("b") and eng.length("a") == 40
+    eng.cache.check_consistency()
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.step([StepEntry("a", [256], [0])])
+    with pytest.raises(ValueError, match="twice"):
+        eng.step([StepEntry("a", [1], [0]), StepEntry("a", [2], [0])])
+    assert eng.cache.free_pages() == free
+
+
+def test_positions_limit(root):
+    d = make_model("A", root, torch.float32, std=0.08)       # 128 positions
+    eng = Engine(d, dtype="float32", page_size=16, num_pages=16, device="cpu", ops=HostOps())
+    eng.step([StepEntry("a", list(range(128)), [])])
+    with pytest.raises(ValueError):
+        eng.step([StepEntry("a", [1], [0])])
+
+
+def test_generation_through_the_entry_point_matches_plain_greedy(root):
+    d = make_model("B", root, torch.float32, std=0.08)
+    cfg, w = plain.load_folder(d)
+    llm = LLM(d, num_blocks=40, block_size=8, max_concurrent=3, device="cpu", dtype="float32",
+              ops=HostOps(), chunk_size=32, max_num_batched_tokens=48)
+    prompts = [random_tokens(n, 1000, 50 + i) for i, n in enumerate([1, 9, 40, 100])]
+    outs = llm.generate_many(prompts, max_new_tokens=6,
+                             sampling_params=SamplingParams(temperature=0.0),
+                             arrival_steps=[0, 0, 1, 3])
+    for p, o in zip(prompts, outs):
+        assert o == plain.greedy(cfg, w, p, 6)
+    assert llm.engine.cache.free_pages() == [40]
+    assert llm.generate(prompts[1], max_new_tokens=4, temperature=0.0) == outs[1][:4]
+
+
+def test_preempted_request_generates_the_same_tokens(root):
+    d = make_model("A", root, torch.float32, std=0.08)
+    prompts = [random_tokens(n, 256, 70 + i) for i, n in enumerate([30, 28, 26])]
+    sp = [SamplingParams(temperature=0.8, seed=100 + i) for i in range(3)]
+    roomy = LLM(d, num_blocks=64, block_size=4, max_concurrent=3, device="cpu", dtype="float32",
+                ops=HostOps())
+    want = roomy.generate_many(prompts, max_new_tokens=20, sampling_params=sp, ignore_eos=True)
+    tight = LLM(d, num_blocks=28, block_size=4, max_concurrent=3, device="cpu", dtype="float32",
+                ops=HostOps())
+    reqs = [tight.make_request(p, max_new_tokens=20, sampling_params=s, ignore_eos=True)
+            for p, s in zip(prompts, sp)]
+    tight.run([(0, r) for r in reqs])
+    assert sum(r.num_preemptions for r in reqs) > 0, "the test is meant to run out of pages"
+    assert [r.output_tokens for r in reqs] == want
+    assert tight.engine.cache.free_pages() == [28]
+
+
+def test_toy_architecture_is_registered_built_and_stepped(root):
+    register_toys()
+    register_architecture(toy_model.ARCH, toy_model.ToyConfig)
+    try:
+        d = toy_model.write_toy_model(root + "/toy")
+        ids = random_tokens(45, toy_model.V, 3)
+        ref = toy_model.plain_logits(d, ids)
+        eng = Engine(d, dtype="float32", page_size=8, max_tokens=128, device="cpu", ops=HostOps())
+        assert len(eng.cache.groups) == 2                      # full keys, and a window of 6
+        got = eng.step([StepEntry("w", ids, list(range(45)))])
+        assert (got - ref).abs().max().item() < 3e-5
+        eng.end("w")
+        rows = []
+        i = 0
+        for c in [5, 2, 11, 1, 1, 9, 16]:
+            rows.append(eng.step([StepEntry("p", ids[i:i + c], list(range(c)))]))
+            i += c
+        assert (torch.cat(rows) - ref).abs().max().item() < 3e-5
+        eng.end("p")
+        assert all(f == eng.num_pages for f in eng.cache.free_pages())
+    finally:
+        unregister_architecture(toy_model.ARCH)
+        unregister_toys()

@@ -1,0 +1,163 @@
+"""Scheduler decisions with a real cache manager on the CPU and no model (no GPU)."""
+
+import pytest
+import torch
+
+from somi_inference_b200.cache import CacheManager
+from somi_inference_b200.engine.scheduler import Request, RequestStatus, Scheduler
+from somi_inference_b200.parts.base import CacheNeeds, PagedKVNeeds
+from somi_inference_b200.sampling import SamplingParams
+
+
+def make(num_pages=8, page_size=4, max_concurrent=4, budget=16, chunk=8, policy="preempt", eos=None):
+    cache = CacheManager([CacheNeeds(paged=PagedKVNeeds(1, 8, None))], [None], num_pages=num_pages,
+                         page_size=page_size, max_requests=max_concurrent, max_positions=64,
+                         dtype=torch.float32, device="cpu")
+    return cache, Scheduler(cache, max_concurrent=max_concurrent, max_num_batched_tokens=budget,
+                            chunk_size=chunk, max_positions=64, eos_token_id=eos, policy=policy)
+
+
+def req(i, n_prompt, max_new=4):
+    return Request(i, list(range(1, n_prompt + 1)), max_new, SamplingParams(temperature=0.0))
+
+
+def run_step(s, token=9):
+    b = s.schedule()
+    done = s.update(b, {i.request.request_id: token for i in b.items if i.samples})
+    return b, done
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    cache, s = make(budget=10, chunk=6)
+    s.add_request(req(0, 15))
+    b, _ = run_step(s)
+    assert [(i.start, i.num_tokens, i.samples) for i in b.items] == [(0, 6, False)]
+    b, _ = run_step(s)
+    assert [(i.start, i.num_tokens, i.samples) for i in b.items] == [(6, 6, False)]
+    b, _ = run_step(s)
+    assert [(i.start, i.num_tokens, i.samples) for i in b.items] == [(12, 3, True)]
+    b, _ = run_step(s)                                   # now decoding
+    assert [(i.start, i.num_tokens, i.samples) for i in b.items] == [(15, 1, True)]
+
+
+def test_decode_tokens_come_first_and_share_the_budget():
+    cache, s = make(budget=8, chunk=8, num_pages=16)
+    s.add_request(req(0, 3))
+    run_step(s)
+    s.add_request(req(1, 20))
+    b, _ = run_step(s)
+    assert [(i.request.request_id, i.num_tokens) for i in b.items] == [(0, 1), (1, 7)]
+    assert b.admitted and b.admitted[0].request_id == 1
+    b, _ = run_step(s)
+    assert [(i.request.request_id, i.num_tokens) for i in b.items] == [(0, 1), (1, 7)]
+
+
+def test_finish_by_length_and_eos_frees_pages():
+    cache, s = make(eos=7)
+    s.add_request(req(0, 5, max_new=3))
+    s.add_request(req(1, 5, max_new=3))
+    run_step(s, token=9)
+    assert cache.free_pages() == [4]
+    b = s.schedule()
+    done = s.update(b, {0: 7, 1: 9})                     # request 0 meets EOS
+    assert [r.request_id for r in done] == [0] and done[0].finish_reason == "eos"
+    assert done[0].output_tokens == [9, 7]               # EOS is kept
+    assert cache.free_pages() == [6]
+    _, done = run_step(s, token=9)
+    assert [r.request_id for r in done] == [1] and done[0].finish_reason == "length"
+    assert cache.free_pages() == [8] and not s.has_unfinished()
+    assert [r.request_id for r in s.drain_finished()] == [0, 1] and s.drain_finished() == []
+
+
+def test_ignore_eos():
+    cache, s = make(eos=7)
+    r = req(0, 2, max_new=3)
+    r.ignore_eos = True
+    s.add_request(r)
+    for _ in range(3):
+        run_step(s, token=7)
+    assert r.status is RequestStatus.FINISHED and r.output_tokens == [7, 7, 7]
+
+
+def test_max_concurrent_and_fcfs():
+    cache, s = make(max_concurrent=2, num_pages=16)
+    for i in range(3):
+        s.add_request(req(i, 2, max_new=2))
+    b, _ = run_step(s)
+    assert [r.request_id for r in b.admitted] == [0, 1] and len(s.waiting) == 1
+    b, done = run_step(s)
+    assert len(done) == 2 and not b.admitted
+    b, _ = run_step(s)
+    assert [r.request_id for r in b.admitted] == [2]
+
+
+def test_impossible_request_is_refused():
+    cache, s = make(num_pages=4, page_size=4)
+    with pytest.raises(ValueError, match="pages"):
+        s.add_request(req(0, 16, max_new=2))             # 17 tokens at its longest > 16
+    with pytest.raises(ValueError, match="positions"):
+        s.add_request(req(1, 60, max_new=10))
+    s.add_request(req(2, 13, max_new=4))                 # exactly 16 tokens: fits
+
+
+def test_head_of_line_blocks_when_pages_are_short():
+    cache, s = make(num_pages=4, page_size=4, budget=32, chunk=32)
+    s.add_request(req(0, 10, max_new=2))
+    s.add_request(req(1, 8, max_new=2))
+    s.add_request(req(2, 2, max_new=2))
+    b, _ = run_step(s)
+    assert [r.request_id for r in b.admitted] == [0]     # 1 needs 2 pages, 1 is free; 2 waits behind it
+    assert [r.request_id for r in s.waiting] == [1, 2]
+
+
+def test_preemption_by_recompute_when_pages_run_out():
+    cache, s = make(num_pages=4, page_size=4, budget=32, chunk=32)
+    a, b_ = req(0, 7, max_new=8), req(1, 7, max_new=8)
+    s.add_request(a)
+    s.add_request(b_)
+    run_step(s)                                          # both prefilled: 2 pages each, pool empty
+    assert cache.free_pages() == [0]
+    batch, _ = run_step(s)                               # both decode into their 8th slot
+    assert not batch.preempted
+    batch = s.schedule()                                 # position 8 needs a third page each
+    assert [r.request_id for r in batch.preempted] == [1]   # the most recently admitted goes
+    assert [i.request.request_id for i in batch.items] == [0]
+    assert b_.status is RequestStatus.WAITING and b_.num_computed == 0 and b_.num_preemptions == 1
+    assert s.waiting[0] is b_ and len(b_.output_tokens) == 2
+    assert not cache.is_registered(1)
+    s.update(batch, {0: 9})
+    cache.check_consistency()
+    # request 0 runs to its end; then request 1 is readmitted and recomputes prompt + 2 outputs
+    while a.status is not RequestStatus.FINISHED:
+        run_step(s)
+    batch, _ = run_step(s)
+    assert [r.request_id for r in batch.admitted] == [1]
+    assert [(i.start, i.num_tokens, i.samples) for i in batch.items] == [(0, 9, True)]
+    while s.has_unfinished():
+        run_step(s)
+    assert len(b_.output_tokens) == 8 and cache.free_pages() == [4]
+
+
+def test_reserve_policy_never_preempts():
+    cache, s = make(num_pages=4, page_size=4, budget=32, chunk=32, policy="reserve")
+    a, b_ = req(0, 7, max_new=8), req(1, 7, max_new=8)      # 14 tokens at most: 4 pages each
+    s.add_request(a)
+    s.add_request(b_)
+    batch, _ = run_step(s)
+    assert [r.request_id for r in batch.admitted] == [0]    # the worst case of both does not fit
+    preempted = 0
+    while s.has_unfinished():
+        batch, _ = run_step(s)
+        preempted += len(batch.preempted)
+    assert preempted == 0 and len(a.output_tokens) == 8 and len(b_.output_tokens) == 8
+
+
+def test_request_validation():
+    with pytest.raises(ValueError):
+        Request(0, [1], 0)
+    with pytest.raises(ValueError):
+        Request(0, [], 3)
+    for bad in (dict(temperature=-1.0), dict(top_k=0), dict(top_p=0.0), dict(top_p=1.5),
+                dict(repetition_penalty=0.0)):
+        with pytest.raises(ValueError):
+            SamplingParams(**bad)
