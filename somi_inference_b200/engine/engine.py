@@ -40,19 +40,35 @@ class Engine:
         The page pool holds `num_pages` pages per group, or enough for
         `max_tokens` tokens (rounded up to whole pages) when that is given.
         """
+        config = load_config(model_dir)
+        spec = config.to_model_spec()
+        declared = declared_tensors(spec)
+        optional = ()
+        if spec.head.params.get("tied"):
+            optional = (spec.head.params["names"]["weight"],)
+        tensors = load_tensors(model_dir, declared, optional=optional)
+        self._setup(config, tensors, dtype=dtype, page_size=page_size, num_pages=num_pages,
+                    max_tokens=max_tokens, max_requests=max_requests, device=device, ops=ops)
+
+    @classmethod
+    def from_tensors(cls, config, tensors: dict, **kwargs) -> "Engine":
+        """An engine over tensors that are already in memory (name -> tensor, any device),
+        e.g. random weights made on the device; `config` is a typed architecture config."""
+        self = cls.__new__(cls)
+        self._setup(config, tensors, **kwargs)
+        return self
+
+    def _setup(self, config, tensors, *, dtype="bfloat16", page_size: int = 16,
+               num_pages: int | None = None, max_tokens: int | None = None,
+               max_requests: int = 16, device="cuda:0", ops=None) -> None:
         self.device = torch.device(device)
         self.dtype = resolve_dtype(dtype)
         if ops is None:
             from ..ops import cuda_ops
             ops = cuda_ops()
         self.ops = ops
-        self.config = load_config(model_dir)
-        self.spec = self.config.to_model_spec()
-        declared = declared_tensors(self.spec)
-        optional = ()
-        if self.spec.head.params.get("tied"):
-            optional = (self.spec.head.params["names"]["weight"],)
-        tensors = load_tensors(model_dir, declared, optional=optional)
+        self.config = config
+        self.spec = config.to_model_spec()
         ctx = BuildContext(dtype=self.dtype, device=self.device, ops=ops)
         with torch.no_grad():
             self.model = Decoder(self.spec, tensors, ctx)

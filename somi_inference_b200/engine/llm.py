@@ -33,15 +33,19 @@ DEFAULT_NUM_BLOCKS = 256       # somi_inference/entrypoints/llm.py:62
 
 
 class LLM:
-    def __init__(self, model: str, *, num_blocks: int = DEFAULT_NUM_BLOCKS,
+    def __init__(self, model: "str | Engine", *, num_blocks: int = DEFAULT_NUM_BLOCKS,
                  block_size: int = DEFAULT_BLOCK_SIZE,
                  max_concurrent: int = DEFAULT_MAX_CONCURRENT,
                  device: torch.device | str | None = None, dtype="float32",
                  max_num_batched_tokens: int = 2048, chunk_size: int = 512,
                  policy: str = "preempt", eos_token_id: int | None = None, ops=None) -> None:
         self.device = torch.device(device) if device is not None else torch.device("cuda:0")
-        self.engine = Engine(model, dtype=dtype, page_size=block_size, num_pages=num_blocks,
-                             max_requests=max_concurrent, device=self.device, ops=ops)
+        if isinstance(model, Engine):         # an engine that was built elsewhere (benchmarks)
+            self.engine = model
+            self.device = model.device
+        else:
+            self.engine = Engine(model, dtype=dtype, page_size=block_size, num_pages=num_blocks,
+                                 max_requests=max_concurrent, device=self.device, ops=ops)
         self.config = self.engine.config
         if eos_token_id is None:
             eos_token_id = getattr(self.config, "eos_token_id", None)
@@ -57,6 +61,9 @@ class LLM:
         self._model_dir = model
         self.steps_run = 0
         self.d2h_bytes_last = 0
+
+    def sampler_h2d_bytes(self) -> int:
+        return self.sampler.h2d_bytes_last
 
     # -------------------------------------------------------------- tokenizer
     def _tok(self):

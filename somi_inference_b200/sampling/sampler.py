@@ -20,6 +20,7 @@ class Sampler:
     def __init__(self, ops, device: torch.device | str) -> None:
         self.ops = ops
         self.device = torch.device(device)
+        self.h2d_bytes_last = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                counters: Sequence[int], seeds: Sequence[int],
@@ -61,6 +62,7 @@ class Sampler:
         h += h % 2
         if n_hist:
             buf[h:h + n_hist] = np.concatenate(toks)
+        self.h2d_bytes_last = buf.nbytes
         dev = torch.from_numpy(buf).to(self.device, non_blocking=True)
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
         self.ops.sample(logits, dev[0:rows].view(torch.float32), dev[r8:r8 + rows],

@@ -1,0 +1,195 @@
+"""Generation through the entry point, long decoding, the first tokens of a sequence, each
+part of a layer alone, and the toy architecture, on the GPU with the CUDA kernels."""
+
+import pytest
+import torch
+
+from tests import replay, toy_model
+from tests.plain import qwen2_plain as plain
+from tests.plain.host_ops import HostOps
+from tests.tiny import PAGE_SIZES, TINY, make_model, random_tokens
+from tests.toy_parts import register_toys, unregister_toys
+
+pytestmark = pytest.mark.gpu
+STD = 0.08
+
+
+@pytest.fixture(scope="module")
+def root(tmp_path_factory):
+    return str(tmp_path_factory.mktemp("gpu_engine"))
+
+
+@pytest.mark.parametrize("name", list(TINY))
+def test_greedy_generation_through_the_entry_point(root, name):
+    from somi_inference_b200 import LLM, SamplingParams
+    d = make_model(name, root, torch.float32, std=STD)
+    cfg, w = plain.load_folder(d)
+    llm = LLM(d, num_blocks=64, block_size=PAGE_SIZES[name], max_concurrent=4, dtype="float32",
+              chunk_size=32, max_num_batched_tokens=64)
+    prompts = [random_tokens(n, cfg["vocab_size"], 50 + i) for i, n in enumerate([1, 9, 40, 100, 33])]
+    outs = llm.generate_many(prompts, max_new_tokens=12,
+                             sampling_params=SamplingParams(temperature=0.0),
+                             arrival_steps=[0, 0, 1, 2, 5])
+    for p, o in zip(prompts, outs):
+        assert o == plain.greedy(cfg, w, p, 12)
+    assert llm.engine.cache.free_pages() == [64] * len(llm.engine.cache.groups)
+    assert llm.generate(prompts[2], max_new_tokens=5, temperature=0.0) == outs[2][:5]
+
+
+def test_temperature_generation_is_reproducible_and_batch_independent(root):
+    from somi_inference_b200 import LLM, SamplingParams
+    d = make_model("B", root, torch.bfloat16, std=STD)
+    llm = LLM(d, num_blocks=64, block_size=8, max_concurrent=4, dtype="float32", chunk_size=32)
+    prompts = [random_tokens(n, 1000, 90 + i) for i, n in enumerate([1, 9, 40, 100])]
+    sps = [SamplingParams(temperature=0.7, seed=5 + i) for i in range(4)]
+    together = llm.generate_many(prompts, max_new_tokens=12, sampling_params=sps)
+    alone = [llm.generate(p, max_new_tokens=12, temperature=0.7, seed=5 + i)
+             for i, p in enumerate(prompts)]
+    assert together == alone
+    assert len({tuple(o) for o in together}) == 4
+
+
+def test_preemption_on_the_gpu_gives_the_same_tokens(root):
+    from somi_inference_b200 import LLM, SamplingParams
+    d = make_model("A", root, torch.float32, std=STD)
+    prompts = [random_tokens(n, 256, 70 + i) for i, n in enumerate([30, 28, 26])]
+    sp = [SamplingParams(temperature=0.0) for _ in range(3)]
+    roomy = LLM(d, num_blocks=64, block_size=4, max_concurrent=3, dtype="float32")
+    want = roomy.generate_many(prompts, max_new_tokens=20, sampling_params=sp, ignore_eos=True)
+    tight = LLM(d, num_blocks=28, block_size=4, max_concurrent=3, dtype="float32")
+    reqs = [tight.make_request(p, max_new_tokens=20, sampling_params=s, ignore_eos=True)
+            for p, s in zip(prompts, sp)]
+    tight.run([(0, r) for r in reqs])
+    assert sum(r.num_preemptions for r in reqs) > 0
+    assert [r.output_tokens for r in reqs] == want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(root, dtype):
+    """A 3-token prompt followed by 300 single-token steps (pages fill and follow one another),
+    and the logits of the very first positions."""
+    from somi_inference_b200.engine import Engine, StepEntry
+    d = make_model("C", root, getattr(torch, dtype), std=STD)
+    cfg, w = plain.load_folder(d)
+    ids = random_tokens(303, cfg["vocab_size"], 4)
+    ref = plain.logits(cfg, w, ids)
+    scale = ref.abs().max().item()
+    atol = 3e-5 if dtype == "float32" else 2e-2 * scale
+    eng = Engine(d, dtype=dtype, page_size=16, max_tokens=320)
+    rows = [eng.step([StepEntry("x", ids[:3], [0, 1, 2])])]
+    for t in ids[3:]:
+        rows.append(eng.step([StepEntry("x", [t], [0])]))
+    got = torch.cat(rows).float().cpu()
+    err = (got - ref).abs().max(dim=1).values
+    assert err.max().item() <= atol, f"first wrong position: {int(torch.nonzero(err > atol)[0])}"
+    assert err[:3].max().item() <= atol
+
+
+def test_parts_alone(root):
+    """Each part of a layer, built through its registry with its own numbers, against the
+    plain formula: norm, feed-forward, embedding and head, attention mixer over a cache."""
+    from somi_inference_b200.cache import CacheManager
+    from somi_inference_b200.config import PartSpec
+    from somi_inference_b200.engine.batch import BatchBuilder, StepEntry
+    from somi_inference_b200.ops import cuda_ops
+    from somi_inference_b200.parts import (EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
+                                           BuildContext)
+    ops = cuda_ops()
+    g = torch.Generator().manual_seed(0)
+    H, I, Vv, T = 96, 200, 301, 23
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 3e-2)):
+        ctx = BuildContext(dtype=dtype, device=torch.device("cuda"), ops=ops)
+        # norm with residual sum
+        wn = 1 + 0.1 * torch.randn(H, generator=g)
+        norm = NORMS.build(PartSpec("rmsnorm", {"size": H, "eps": 2e-5, "names": {"weight": "n"}}),
+                           {"n": ctx.place(wn, matrix=False)}, ctx)
+        res, delta = torch.randn(T, H, generator=g), torch.randn(T, H, generator=g).to(dtype)
+        r = res.clone().cuda()
+        out = norm.forward(r, delta.cuda())
+        want = plain.rms_norm(res + delta.float(), wn, 2e-5)
+        assert (out.float().cpu() - want).abs().max() < tol * 4
+        assert torch.equal(r.cpu(), res + delta.float())
+        # feed-forward
+        ws = {k: 0.1 * torch.randn(s, generator=g) for k, s in
+              (("p.mlp.gate_proj.weight", (I, H)), ("p.mlp.up_proj.weight", (I, H)),
+               ("p.mlp.down_proj.weight", (H, I)))}
+        ws = {k: v.to(dtype).float() for k, v in ws.items()}
+        ff = FEED_FORWARDS.build(PartSpec("swiglu", {
+            "hidden_size": H, "intermediate_size": I,
+            "names": {"gate_weight": "p.mlp.gate_proj.weight", "up_weight": "p.mlp.up_proj.weight",
+                      "down_weight": "p.mlp.down_proj.weight"}}),
+            {k: ctx.place(v, matrix=True) for k, v in ws.items()}, ctx)
+        x = torch.randn(T, H, generator=g).to(dtype)
+        y = ff.forward(x.cuda(), None)
+        assert (y.float().cpu() - plain.swiglu(x.float(), ws, "p")).abs().max() < tol * 4
+        # embedding and heads (tied and untied)
+        table = (0.1 * torch.randn(Vv, H, generator=g)).to(dtype).float()
+        head_w = (0.1 * torch.randn(Vv, H, generator=g)).to(dtype).float()
+        placed = {"e": ctx.place(table, matrix=True), "h": ctx.place(head_w, matrix=True)}
+        emb = EMBEDDINGS.build(PartSpec("token_embedding", {"vocab_size": Vv, "hidden_size": H,
+                                                            "names": {"weight": "e"}}), placed, ctx)
+        ids = torch.randint(0, Vv, (T,), generator=g, dtype=torch.int32)
+        assert torch.equal(emb.forward(ids.cuda()).cpu(), table[ids.long()])
+        for tied, wm in ((True, table), (False, head_w)):
+            head = HEADS.build(PartSpec("lm_head", {"vocab_size": Vv, "hidden_size": H, "tied": tied,
+                                                    "names": {"weight": "h", "tied_to": "e"}}),
+                               placed, ctx)
+            lg = head.forward(x.cuda())
+            assert lg.dtype == torch.float32
+            assert (lg.cpu() - x.float() @ wm.T).abs().max() < tol * 4
+        # attention mixer: two steps over its own cache against the plain block
+        nq, nkv, hd = 6, 2, 16
+        cfg = {"num_attention_heads": nq, "num_key_value_heads": nkv, "head_dim": hd, "hidden_size": H}
+        wa = {}
+        for nme, shp in (("q_proj.weight", (nq * hd, H)), ("k_proj.weight", (nkv * hd, H)),
+                         ("v_proj.weight", (nkv * hd, H)), ("o_proj.weight", (H, nq * hd)),
+                         ("q_proj.bias", (nq * hd,)), ("k_proj.bias", (nkv * hd,)),
+                         ("v_proj.bias", (nkv * hd,))):
+            wa[f"p.self_attn.{nme}"] = (0.15 * torch.randn(shp, generator=g)).to(dtype).float()
+        names = {f"{a}_{b}": f"p.self_attn.{a}_proj.{b}" for a in "qkvo" for b in ("weight", "bias")}
+        mixer = MIXERS.build(PartSpec("attention", {
+            "hidden_size": H, "num_heads": nq, "num_kv_heads": nkv, "head_dim": hd, "qkv_bias": True,
+            "out_bias": False, "window": 9, "names": names,
+            "position": PartSpec("rope", {"head_dim": hd, "theta": 777.0, "max_positions": 64})}),
+            {k: ctx.place(v, matrix=v.dim() == 2) for k, v in wa.items()}, ctx)
+        mgr = CacheManager([mixer.cache_needs()], [None], num_pages=8, page_size=4, max_requests=2,
+                           max_positions=64, dtype=dtype, device="cuda")
+        builder = BatchBuilder(mgr, device="cuda", q_tile_sizes=ops.q_tile_sizes)
+        h = torch.randn(T, H, generator=g).to(dtype)
+        cos, sin = plain.rope_tables(hd, 777.0, T)
+        want = plain.attention_block(h.float(), wa, "p", cfg, cos, sin, 9)
+        mgr.register("r")
+        outs = []
+        for a, b in ((0, 14), (14, 15), (15, T)):
+            mgr.reserve("r", b - a)
+            batch, _ = builder.build([StepEntry("r", [0] * (b - a), [])])
+            outs.append(mixer.forward(h[a:b].cuda(), batch, mgr.view(0), True))
+            mgr.commit("r")
+        assert (torch.cat(outs).float().cpu() - want).abs().max() < tol * 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_on_the_gpu(root, dtype):
+    """A mixer with state of its own, a routed feed-forward and another position encoding, all
+    defined by the tests, run through the engine with the CUDA kernels for everything else."""
+    from somi_inference_b200.config import register_architecture, unregister_architecture
+    from somi_inference_b200.engine import Engine, StepEntry
+    register_toys()
+    register_architecture(toy_model.ARCH, toy_model.ToyConfig)
+    try:
+        d = toy_model.write_toy_model(root + f"/toy_{dtype}", dtype=getattr(torch, dtype),
+                                      n_experts=3 if dtype == "float32" else 1)
+        reqs = {f"t{i}": random_tokens(n, toy_model.V, 20 + i) for i, n in enumerate([45, 70, 12, 90, 33])}
+        ref = {k: toy_model.plain_logits(d, v) for k, v in reqs.items()}
+        scale = max(v.abs().max().item() for v in ref.values())
+        atol = 3e-5 if dtype == "float32" else 2e-2 * scale
+        for mode in (replay.whole, replay.portions, replay.mixed):
+            steps, max_tokens = mode(reqs)
+            eng = Engine(d, dtype=dtype, page_size=8, max_tokens=max_tokens)
+            assert len(eng.cache.groups) == 2
+            got = replay.run_steps(eng, steps)
+            replay.compare(got, ref, atol, f"toy/{dtype}/{mode.__name__}")
+            assert all(f == eng.num_pages for f in eng.cache.free_pages())
+    finally:
+        unregister_architecture(toy_model.ARCH)
+        unregister_toys()

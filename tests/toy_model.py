@@ -55,7 +55,7 @@ class ToyConfig:
                 swiglu("l0", 72), norm("l0.n1"), norm("l0.n2")),
             LayerSpec("l1", PartSpec("toy_decay", {"hidden_size": H, "state_size": 24, "decay": 0.8,
                                                    "names": {"w_in": "l1.w_in", "w_out": "l1.w_out"}}),
-                      PartSpec("toy_routed", {"hidden_size": H, "n_experts": 3, "inner": 20,
+                      PartSpec("toy_routed", {"hidden_size": H, "n_experts": d["n_experts"], "inner": 20,
                                               "names": {"router": "l1.router", "w1": "l1.w1",
                                                         "w2": "l1.w2"}}),
                       norm("l1.n1"), norm("l1.n2")),
@@ -72,9 +72,12 @@ class ToyConfig:
                                               "names": {"weight": "head", "tied_to": "emb"}}))
 
 
-def write_toy_model(out_dir: str, seed: int = 5, dtype=torch.float32) -> str:
+def write_toy_model(out_dir: str, seed: int = 5, dtype=torch.float32, n_experts: int = 3) -> str:
+    """`n_experts` = 1 switches the hard top-1 routing off: under bfloat16 rounding a token
+    whose two best router logits nearly tie may legitimately go to the other expert, which no
+    tolerance on logits can express; the bfloat16 test therefore routes trivially."""
     os.makedirs(out_dir, exist_ok=True)
-    raw = {"architectures": [ARCH], "theta": 5000.0, "max_positions": 256}
+    raw = {"architectures": [ARCH], "theta": 5000.0, "max_positions": 256, "n_experts": n_experts}
     with open(os.path.join(out_dir, "config.json"), "w") as f:
         json.dump(raw, f)
     g = torch.Generator().manual_seed(seed)
@@ -129,7 +132,7 @@ def plain_logits(model_dir: str, ids: list[int]) -> torch.Tensor:
     def l1(x):
         x = x + ToyDecayMixer.plain(plain.rms_norm(x, w["l1.n1"], EPS), w["l1.w_in"], w["l1.w_out"], 0.8)
         return x + ToyRoutedFF.plain(plain.rms_norm(x, w["l1.n2"], EPS), w["l1.router"],
-                                     w["l1.w1"].view(3, 20, H), w["l1.w2"].view(3, H, 20))
+                                     w["l1.w1"].view(-1, 20, H), w["l1.w2"].view(-1, H, 20))
 
     def l2(x):
         a, _ = _attention(plain.rms_norm(x, w["l2.n1"], EPS), w, "l2", 2, 1, 32, 6, shift)
