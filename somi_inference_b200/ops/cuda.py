@@ -59,6 +59,10 @@ class CudaOps:
         self.lib.somi_attention_generic_q_tile.restype = ctypes.c_int
         self.generic_q_tile = int(self.lib.somi_attention_generic_q_tile())
         self.q_tile_sizes = (self.generic_q_tile,)
+        self.lib.somi_decode_chunk.restype = ctypes.c_int
+        self.decode_chunk = int(self.lib.somi_decode_chunk())
+        self._workspace = None
+        self._retired: list = []
         self.launches = 0     # kernels of this library launched so far
 
     # ------------------------------------------------------------------ util
@@ -114,21 +118,60 @@ class CudaOps:
             _ptr(slot_map), _ptr(kcache), _ptr(vcache), ctypes.c_int(page_size), self._stream())
         self._done(rc, "rope_store")
 
+    def _scratch(self, n_floats: int, device) -> torch.Tensor:
+        """Float32 scratch that outlives the call (kernels of a captured graph keep its address)."""
+        if self._workspace is None or self._workspace.numel() < n_floats:
+            if self._workspace is not None:
+                self._retired.append(self._workspace)
+            self._workspace = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
+        return self._workspace
+
+    def decode_supported(self, nq: int, nkv: int, hd: int, dtype) -> bool:
+        return dtype == torch.bfloat16 and bool(self.lib.somi_decode_supported(
+            ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd)))
+
     def paged_attention(self, qkv, kcache, vcache, batch, group, nq, nkv, hd, scale, window,
                         out) -> None:
+        """Attention of every token of the step over the cache (keys/values already stored).
+
+        Single-token requests go to the split-KV kernel where it takes the geometry
+        (bfloat16, head sizes 32/64/128, at most 16 query heads per kv head); portions of
+        prompts, float32 and every other size go to the generic kernel.
+        """
         _check(qkv, kcache, vcache, out, group.block_table)
         assert kcache.dtype == qkv.dtype
+        page_size = kcache.shape[2]
+        win = int(window) if window else 0
+        n_decode = batch.num_requests - batch.num_prefill_requests
         tiles = batch.tiles[self.generic_q_tile]
-        rc = self.lib.somi_paged_attention_generic(
-            _ptr(qkv), _code(qkv), ctypes.c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache),
-            _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
-            _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
-            ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(batch.num_prefill_tokens),
-            ctypes.c_int(batch.num_requests - batch.num_prefill_requests),
-            ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(kcache.shape[2]),
-            ctypes.c_float(scale), ctypes.c_int(int(window) if window else 0), _ptr(out),
-            self._stream())
-        self._done(rc, "paged_attention")
+        split = n_decode > 0 and self.decode_supported(nq, nkv, hd, qkv.dtype)
+        n_generic_decode = 0 if split else n_decode
+        if tiles.shape[0] + n_generic_decode > 0:
+            rc = self.lib.somi_paged_attention_generic(
+                _ptr(qkv), _code(qkv), ctypes.c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache),
+                _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
+                ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(batch.num_prefill_tokens),
+                ctypes.c_int(n_generic_decode), ctypes.c_int(nq), ctypes.c_int(nkv),
+                ctypes.c_int(hd), ctypes.c_int(page_size), ctypes.c_float(scale),
+                ctypes.c_int(win), _ptr(out), self._stream())
+            self._done(rc, "paged_attention")
+        if split:
+            chunk = self.decode_chunk
+            max_splits = -(-group.width * page_size // chunk)
+            n_o = n_decode * nq * max_splits * hd
+            ws = self._scratch(n_o + n_decode * nq * max_splits * 2, qkv.device)
+            rc = self.lib.somi_paged_attention_decode(
+                _ptr(qkv), ctypes.c_int(qkv.shape[1]), ctypes.c_int(batch.num_prefill_tokens),
+                ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(n_decode), _ptr(kcache),
+                _ptr(vcache), _ptr(group.block_table), ctypes.c_int(group.width),
+                _ptr(batch.ctx_len), ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd),
+                ctypes.c_int(page_size), ctypes.c_float(scale), ctypes.c_int(win),
+                ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(ws.data_ptr() + 4 * n_o),
+                ctypes.c_int(max_splits), _ptr(out), self._stream())
+            self._done(rc, "paged_attention_decode")
+            if max_splits > 1:
+                self.launches += 1
 
     def silu_mul(self, gu: torch.Tensor, out: torch.Tensor) -> None:
         _check(gu, out)

@@ -169,3 +169,36 @@ def test_attention_far_key_and_window_edge(ops, dtype, window):
         seen = window is None or spot > qpos - window
         close = torch.allclose(got, planted, rtol=2e-2, atol=2e-2)
         assert close == seen, f"key at {spot}: seen={seen}, output equals its value: {close}"
+
+
+DECODE_CASES = [
+    # nq nkv hd ps window ctx lengths (each request brings one token)
+    (14, 2, 64, 16, None, [0, 1, 126, 127, 128, 129, 255, 256, 1000, 2047]),
+    (28, 4, 128, 16, None, [5, 127, 128, 700, 2048]),
+    (16, 1, 64, 8, None, [300, 17]),
+    (3, 3, 32, 64, None, [130, 64, 63]),
+    (14, 2, 64, 16, 200, [10, 199, 200, 201, 500, 383, 384, 385]),
+    (8, 4, 128, 32, 128, [127, 128, 129, 1000]),
+]
+
+
+@pytest.mark.parametrize("case", DECODE_CASES, ids=[f"d{i}" for i in range(len(DECODE_CASES))])
+def test_split_kv_decode_attention(ops, case):
+    """Single-token requests around the 128-key chunk edges, with and without a window, beside
+    one prompt portion; bfloat16 goes through the split-KV kernel."""
+    nq, nkv, hd, ps, window, ctxs = case
+    assert ops.decode_supported(nq, nkv, hd, torch.bfloat16)
+    reqs = [(c, 1) for c in ctxs] + [(40, 9)]
+    mgr, batch, qkv, view, _ = attention_case(ops, nq=nq, nkv=nkv, hd=hd, page_size=ps,
+                                              window=window, requests=reqs, dtype=torch.bfloat16,
+                                              seed=7)
+    out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    before = ops.launches
+    ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
+                        hd ** -0.5, window, out)
+    assert ops.launches - before >= 2      # generic kernel for the portion, split kernel for the rest
+    ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
+    cb = batch_to_cpu(batch)
+    HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), cb, cb.groups[0], nq, nkv,
+                         hd, hd ** -0.5, window, ref)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(torch.bfloat16))
