@@ -86,6 +86,7 @@ class BatchBuilder:
         self.q_tile_sizes = tuple(q_tile_sizes)
         self.vocab_size = vocab_size
         self.max_positions = max_positions
+        self.width_step = max(1, 512 // cache.page_size)     # table columns come in steps of 512 tokens
         self._capacity = 0
         self._turn = 0
         self._alloc(capacity_ints)
@@ -172,7 +173,10 @@ class BatchBuilder:
         tables = []
         slot_maps = []
         for gi in range(len(self.cache.groups)):
+            # the width is rounded up so that the layout, and with it a captured graph, stays
+            # the same while requests grow by a few hundred tokens
             width = int(max(-(-int(kv_len.max()) // ps), 1))
+            width = min(-(-width // self.width_step) * self.width_step, self.cache.max_blocks)
             table = self.cache.block_tables(gi, slots, width)
             page = table[token_req, positions // ps].astype(np.int64)
             if (page < 0).any():

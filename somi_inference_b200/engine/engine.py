@@ -34,7 +34,7 @@ class Engine:
     def __init__(self, model_dir: str, *, dtype="bfloat16", page_size: int = 16,
                  num_pages: int | None = None, max_tokens: int | None = None,
                  max_requests: int = 16, device: str | torch.device = "cuda:0",
-                 ops=None) -> None:
+                 ops=None, use_graphs: bool = True) -> None:
         """Load `model_dir` (config.json + safetensors) and lay out its cache.
 
         The page pool holds `num_pages` pages per group, or enough for
@@ -48,7 +48,8 @@ class Engine:
             optional = (spec.head.params["names"]["weight"],)
         tensors = load_tensors(model_dir, declared, optional=optional)
         self._setup(config, tensors, dtype=dtype, page_size=page_size, num_pages=num_pages,
-                    max_tokens=max_tokens, max_requests=max_requests, device=device, ops=ops)
+                    max_tokens=max_tokens, max_requests=max_requests, device=device, ops=ops,
+                    use_graphs=use_graphs)
 
     @classmethod
     def from_tensors(cls, config, tensors: dict, **kwargs) -> "Engine":
@@ -60,7 +61,8 @@ class Engine:
 
     def _setup(self, config, tensors, *, dtype="bfloat16", page_size: int = 16,
                num_pages: int | None = None, max_tokens: int | None = None,
-               max_requests: int = 16, device="cuda:0", ops=None) -> None:
+               max_requests: int = 16, device="cuda:0", ops=None,
+               use_graphs: bool = True) -> None:
         self.device = torch.device(device)
         self.dtype = resolve_dtype(dtype)
         if ops is None:
@@ -88,6 +90,11 @@ class Engine:
                                     vocab_size=self.spec.vocab_size,
                                     max_positions=self.spec.max_positions)
         self.last_batch: StepBatch | None = None
+        self.use_graphs = use_graphs
+        self.max_graphs = 64
+        self._graphs: dict[tuple, tuple] = {}
+        self._seen: dict[tuple, int] = {}
+        self._graph_pool = None
 
     # ------------------------------------------------------------------ step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -129,9 +136,37 @@ class Engine:
         return self._run(batch)
 
     def _run(self, batch: StepBatch) -> torch.Tensor:
-        with torch.no_grad():
-            logits = self.model.forward(batch, self.cache)
+        """Forward pass of one batch.  Steps that hold only single-token requests are launch
+        bound, so their kernel sequence is captured in a CUDA graph the second time a layout
+        (batch size, table width, wanted rows) is seen and replayed from then on; the batch
+        descriptor lives at fixed device addresses, so a replay reads the new step's data."""
         self.last_batch = batch
+        graphable = (self.use_graphs and batch.num_prefill_requests == 0
+                     and self.device.type == "cuda" and self.model.graph_safe)
+        if not graphable:
+            with torch.no_grad():
+                return self.model.forward(batch, self.cache)
+        key = batch.layout_key
+        entry = self._graphs.get(key)
+        if entry is not None:
+            graph, logits, launches = entry
+            graph.replay()
+            self.ops.launches += launches
+            return logits.clone()       # the graph's own output buffer is overwritten by the next replay
+        with torch.no_grad():
+            logits = self.model.forward(batch, self.cache)      # also warms up the libraries
+        self._seen[key] = self._seen.get(key, 0) + 1
+        if self._seen[key] >= 2 and len(self._graphs) < self.max_graphs:
+            # Capturing runs nothing; recording the same step again is harmless because a step
+            # only writes the cache slots of its own tokens, with the same values.
+            before = self.ops.launches
+            graph = torch.cuda.CUDAGraph()
+            with torch.no_grad(), torch.cuda.graph(graph, pool=self._graph_pool):
+                static_logits = self.model.forward(batch, self.cache)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            self._graphs[key] = (graph, static_logits, self.ops.launches - before)
+            self.ops.launches = before
         return logits
 
     def end(self, request: object) -> None:

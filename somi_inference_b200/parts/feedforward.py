@@ -17,6 +17,8 @@ from .registry import FEED_FORWARDS
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU:
+    graph_safe = True     # launches kernels only; nothing is decided on the host per step
+
     @staticmethod
     def declare(params) -> list[TensorDecl]:
         n = names_of(params)

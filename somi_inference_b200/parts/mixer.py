@@ -23,6 +23,8 @@ from .registry import MIXERS, POSITION_ENCODINGS
 
 @MIXERS.register("attention")
 class AttentionMixer:
+    graph_safe = True     # launches kernels only; nothing is decided on the host per step
+
     @staticmethod
     def declare(params) -> list[TensorDecl]:
         n = names_of(params)

@@ -50,6 +50,9 @@ class Decoder:
         self.final_norm = NORMS.build(spec.final_norm, placed, ctx)
         self.head = HEADS.build(spec.head, placed, ctx)
         self.schedule = spec.schedule
+        # a step can be captured in a CUDA graph only if no part plans on the host per step
+        self.graph_safe = all(getattr(p, "graph_safe", False)
+                              for b in self.layers for p in (b.mixer, b.feed_forward))
 
     def _build_layer(self, layer: LayerSpec, placed):
         return ARRANGEMENTS.get(layer.arrangement)(
