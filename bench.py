@@ -146,15 +146,15 @@ def model_bytes_and_flops(cfg, layers: int) -> dict:
             "attn_flops_per_layer": lambda T: 4 * nq * hd * (T * (T + 1) // 2)}
 
 
-def fill_context(eng, batch: int, vocab: int, tag: str):
-    """Prefill `batch` requests to CONTEXT tokens through the step function."""
+def fill_context(eng, batch: int, vocab: int, tag: str, context: int = CONTEXT):
+    """Prefill `batch` requests to `context` tokens through the step function."""
     import torch
 
     from somi_inference_b200.engine import StepEntry
     g = torch.Generator().manual_seed(1)
     ids = []
     for b in range(batch):
-        toks = torch.randint(0, vocab, (CONTEXT,), generator=g).tolist()
+        toks = torch.randint(0, vocab, (context,), generator=g).tolist()
         eng.step([StepEntry((tag, b), toks, [])])
         ids.append((tag, b))
     torch.cuda.synchronize()
@@ -200,6 +200,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--only", choices=["decode", "prefill"], default=None,
+                    help="run only this phase and print its figures (for profiling runs)")
+    ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per request")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -227,6 +230,14 @@ def main() -> int:
     pk, pk_kind = peaks()
     V = cfg.vocab_size
 
+    if args.only == "decode":
+        reqs = fill_context(eng, args.batch, V, "main", args.context)
+        ms, launches, _ = time_decode(eng, sampler, reqs, V, args.steps, args.warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context,
+                          "ms_per_step": round(ms, 4), "tokens_per_s": round(args.batch / ms * 1e3, 1),
+                          "gpu_launches": int(launches)}))
+        return 0
+
     # ---- prefill of 2,048 tokens (one request, one step), timed over a few repetitions
     g = torch.Generator().manual_seed(3)
     prompt = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
@@ -246,6 +257,9 @@ def main() -> int:
     prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
                "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", **prefill}))
+        return 0
 
     # ---- decode at the headline batch, device-timed
     reqs = fill_context(eng, args.batch, V, "main")

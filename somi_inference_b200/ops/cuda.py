@@ -58,7 +58,9 @@ class CudaOps:
         self.lib = ctypes.CDLL(self.lib_path)
         self.lib.somi_attention_generic_q_tile.restype = ctypes.c_int
         self.generic_q_tile = int(self.lib.somi_attention_generic_q_tile())
-        self.q_tile_sizes = (self.generic_q_tile,)
+        self.lib.somi_prefill_q_tile.restype = ctypes.c_int
+        self.prefill_q_tile = int(self.lib.somi_prefill_q_tile())
+        self.q_tile_sizes = (self.generic_q_tile, self.prefill_q_tile)
         self.lib.somi_decode_chunk.restype = ctypes.c_int
         self.decode_chunk = int(self.lib.somi_decode_chunk())
         self._workspace = None
@@ -126,6 +128,10 @@ class CudaOps:
             self._workspace = torch.empty(max(n_floats, 1 << 20), dtype=torch.float32, device=device)
         return self._workspace
 
+    def prefill_supported(self, nq: int, nkv: int, hd: int, dtype) -> bool:
+        return dtype == torch.bfloat16 and bool(self.lib.somi_prefill_supported(
+            ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd)))
+
     def decode_supported(self, nq: int, nkv: int, hd: int, dtype) -> bool:
         return dtype == torch.bfloat16 and bool(self.lib.somi_decode_supported(
             ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd)))
@@ -134,23 +140,35 @@ class CudaOps:
                         out) -> None:
         """Attention of every token of the step over the cache (keys/values already stored).
 
-        Single-token requests go to the split-KV kernel where it takes the geometry
-        (bfloat16, head sizes 32/64/128, at most 16 query heads per kv head); portions of
-        prompts, float32 and every other size go to the generic kernel.
+        In bfloat16 with head sizes 32/64/128, portions of prompts go to the tensor-core
+        prefill kernel and single-token requests to the split-KV kernel (at most 16 query
+        heads per kv head); float32 and every other size go to the generic kernel.
         """
         _check(qkv, kcache, vcache, out, group.block_table)
         assert kcache.dtype == qkv.dtype
         page_size = kcache.shape[2]
         win = int(window) if window else 0
         n_decode = batch.num_requests - batch.num_prefill_requests
-        tiles = batch.tiles[self.generic_q_tile]
         split = n_decode > 0 and self.decode_supported(nq, nkv, hd, qkv.dtype)
+        tensor_core_prefill = (batch.num_prefill_requests > 0
+                               and self.prefill_supported(nq, nkv, hd, qkv.dtype))
+        if tensor_core_prefill:
+            tiles = batch.tiles[self.prefill_q_tile]
+            rc = self.lib.somi_paged_attention_prefill(
+                _ptr(qkv), ctypes.c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache),
+                _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), ctypes.c_int(nq),
+                ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
+                ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
+            self._done(rc, "paged_attention_prefill")
+        tiles = batch.tiles[self.generic_q_tile]
+        n_generic_tiles = 0 if tensor_core_prefill else tiles.shape[0]
         n_generic_decode = 0 if split else n_decode
-        if tiles.shape[0] + n_generic_decode > 0:
+        if n_generic_tiles + n_generic_decode > 0:
             rc = self.lib.somi_paged_attention_generic(
                 _ptr(qkv), _code(qkv), ctypes.c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache),
                 _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
-                _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
+                _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(n_generic_tiles),
                 ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(batch.num_prefill_tokens),
                 ctypes.c_int(n_generic_decode), ctypes.c_int(nq), ctypes.c_int(nkv),
                 ctypes.c_int(hd), ctypes.c_int(page_size), ctypes.c_float(scale),

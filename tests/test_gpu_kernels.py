@@ -196,7 +196,36 @@ def test_split_kv_decode_attention(ops, case):
     before = ops.launches
     ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
                         hd ** -0.5, window, out)
-    assert ops.launches - before >= 2      # generic kernel for the portion, split kernel for the rest
+    assert ops.launches - before >= 2      # one kernel for the portion, the split kernel for the rest
+    ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
+    cb = batch_to_cpu(batch)
+    HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), cb, cb.groups[0], nq, nkv,
+                         hd, hd ** -0.5, window, ref)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(torch.bfloat16))
+
+
+PREFILL_CASES = [
+    # nq nkv hd ps window requests (ctx, q)
+    (14, 2, 64, 16, None, [(0, 200), (100, 64), (37, 2), (63, 65), (0, 1), (500, 3)]),
+    (28, 4, 128, 16, None, [(0, 130), (1000, 70), (64, 64)]),
+    (6, 3, 32, 8, 24, [(0, 90), (50, 30), (23, 2), (5, 70)]),
+    (4, 1, 64, 32, 100, [(0, 300), (150, 129)]),
+    (2, 2, 128, 64, None, [(3, 61), (0, 64), (0, 65)]),
+]
+
+
+@pytest.mark.parametrize("case", PREFILL_CASES, ids=[f"p{i}" for i in range(len(PREFILL_CASES))])
+def test_tensor_core_prefill_attention(ops, case):
+    """Portions with and without cached context, around the 64-row and 64-key tile edges,
+    windows shorter and longer than a tile; bfloat16 goes through the tensor-core kernel."""
+    nq, nkv, hd, ps, window, reqs = case
+    assert ops.prefill_supported(nq, nkv, hd, torch.bfloat16)
+    mgr, batch, qkv, view, _ = attention_case(ops, nq=nq, nkv=nkv, hd=hd, page_size=ps,
+                                              window=window, requests=reqs, dtype=torch.bfloat16,
+                                              seed=11)
+    out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
+                        hd ** -0.5, window, out)
     ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
     cb = batch_to_cpu(batch)
     HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), cb, cb.groups[0], nq, nkv,
