@@ -44,6 +44,7 @@ class PagedView:
     values: torch.Tensor       # same shape
     page_size: int
     window: int | None
+    storage: torch.Tensor | None = None   # the group's whole tensor (for tensor maps over it)
 
 
 @dataclass
@@ -111,7 +112,7 @@ class CacheManager:
                     if run in g.runs:
                         r = g.runs.index(run)
                         view.paged = PagedView(gi, g.storage[r, 0], g.storage[r, 1],
-                                               page_size, g.needs.window)
+                                               page_size, g.needs.window, g.storage)
             if needs.state is not None:
                 for name, (shape, sdtype) in needs.state.tensors.items():
                     view.state[name] = torch.zeros((max_requests, *shape), dtype=sdtype,

@@ -1,0 +1,335 @@
+// Split-KV grouped-query decode attention whose keys and values arrive by TMA.
+//
+// Same decomposition and arithmetic as attention_decode.cu (one CTA = request x kv head x
+// 128 keys, all query heads of the group as MMA rows, partial results merged by a second
+// kernel), but the cache pages are fetched by bulk tensor copies: one thread issues, per page,
+// one `cp.async.bulk.tensor.2d` per 64-element half of the head for keys and one for values;
+// the 128-byte hardware swizzle lays the rows out conflict-free for ldmatrix, and two
+// mbarriers tell the warps when the keys and when the values have landed.  No thread computes
+// a per-element address.  The cache group's whole storage is one 2-D tensor map
+// [rows = runs * 2 * pages * kv_heads * page_size, head_dim]; a page of one kv head is
+// page_size consecutive rows.
+//
+// Needs head_dim 64 or 128 and a page size that is a multiple of 8 and divides 128.
+#include "mma.cuh"
+#include "tma.cuh"
+
+namespace somi {
+
+constexpr int kTdChunk = 128;
+constexpr int kTdThreads = 128;
+constexpr int kTdRows = 16;
+constexpr int kHalfBytes = kTdChunk * 128;     // one 64-element half of a 128-key tile
+
+__device__ int g_decode_tma_error = 0;          // set when a bounded wait ran out
+
+// byte offset of 16-byte chunk `chunk` (0 .. HD/8) of key `key` in a tile made of HD/64 halves
+__device__ __forceinline__ int tma_tile_offset(int key, int chunk) {
+    return (chunk >> 3) * kHalfBytes + key * 128 + (((chunk & 7) ^ (key & 7)) << 4);
+}
+
+struct TdRange {
+    int kv_len, first_key, first_split, n_splits;
+};
+__device__ __forceinline__ TdRange td_range(int ctx_len, int window) {
+    TdRange r;
+    r.kv_len = ctx_len + 1;
+    r.first_key = window > 0 ? max(0, ctx_len - window + 1) : 0;
+    r.first_split = r.first_key / kTdChunk;
+    r.n_splits = (r.kv_len + kTdChunk - 1) / kTdChunk;
+    return r;
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kTdThreads)
+paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
+                        const __nv_bfloat16* __restrict__ qkv, int row_stride, int row_base,
+                        int req_base, long long k_row0, long long v_row0,
+                        const int* __restrict__ block_table, int bt_stride,
+                        const int* __restrict__ ctx_len, int nq, int nkv, int page_size,
+                        float scale_log2e, int window, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int max_splits,
+                        __nv_bfloat16* __restrict__ out) {
+    constexpr int CPR = HD / 8;
+    constexpr int HALVES = HD / 64;
+    constexpr int TILE = HALVES * kHalfBytes;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    unsigned char* Ks = base;                     // HALVES x [128][64] bf16, hardware swizzle
+    unsigned char* Vs = Ks + TILE;
+    unsigned char* Qs = Vs + TILE;                // [16][HD] bf16, software swizzle
+    __shared__ __align__(8) unsigned long long bars[2];
+    __shared__ float m_s[4][kTdRows], l_s[4][kTdRows];
+
+    const int split = blockIdx.x, kvh = blockIdx.y, i = blockIdx.z;
+    const int req = req_base + i, row = row_base + i;
+    const int G = nq / nkv;
+    const TdRange rg = td_range(ctx_len[req], window);
+    if (split < rg.first_split || split >= rg.n_splits) return;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int k0 = split * kTdChunk;
+    const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
+    const uint32_t bar_k = smem_u32(&bars[0]), bar_v = smem_u32(&bars[1]);
+
+    // pages of this chunk that hold keys the request reads
+    const int pages_in_chunk = kTdChunk / page_size;
+    const int first_page = max(k0, rg.first_key) / page_size;             // absolute index
+    const int last_page = (min(k0 + kTdChunk, rg.kv_len) - 1) / page_size;
+    const int chunk_page0 = k0 / page_size;
+
+    if (tid == 0) {
+        mbar_init(bar_k, 1);
+        mbar_init(bar_v, 1);
+        mbar_fence_init();
+    }
+    // V rows of pages that are not loaded must not hold stale non-finite bit patterns
+    for (int p = 0; p < pages_in_chunk; ++p) {
+        const int ap = chunk_page0 + p;
+        if (ap >= first_page && ap <= last_page) continue;
+        for (int c = tid; c < page_size * CPR; c += kTdThreads) {
+            const int r = p * page_size + c / CPR, ch = c % CPR;
+            *reinterpret_cast<uint4*>(Vs + tma_tile_offset(r, ch)) = make_uint4(0, 0, 0, 0);
+        }
+    }
+    // Q: rows of the group's heads, zero rows up to 16
+    const __nv_bfloat16* qrow = qkv + static_cast<size_t>(row) * row_stride + static_cast<size_t>(kvh) * G * HD;
+    for (int c = tid; c < kTdRows * CPR; c += kTdThreads) {
+        const int r = c / CPR, ch = c - r * CPR;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < G) v = *reinterpret_cast<const uint4*>(qrow + r * HD + ch * 8);
+        *reinterpret_cast<uint4*>(Qs + swizzled_offset<HD>(r, ch)) = v;
+    }
+    fence_proxy_async();        // the zero fill above is ordered before the async proxy's writes
+    __syncthreads();
+
+    if (tid == 0) {
+        const uint32_t bytes = static_cast<uint32_t>(last_page - first_page + 1) * page_size * HD * 2;
+        mbar_expect_tx(bar_k, bytes);
+        for (int ap = first_page; ap <= last_page; ++ap) {
+            const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
+            const int r = (ap - chunk_page0) * page_size;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_2d(smem_u32(Ks + h * kHalfBytes + r * 128), &kv_map, h * 64,
+                            static_cast<int>(k_row0 + prow), bar_k);
+        }
+        mbar_expect_tx(bar_v, bytes);
+        for (int ap = first_page; ap <= last_page; ++ap) {
+            const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
+            const int r = (ap - chunk_page0) * page_size;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_2d(smem_u32(Vs + h * kHalfBytes + r * 128), &kv_map, h * 64,
+                            static_cast<int>(v_row0 + prow), bar_v);
+        }
+    }
+
+    bool ok_wait = mbar_wait(bar_k, 0);
+    // ---- S = Q K^T for this warp's 32 keys
+    float s[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) s[a][b] = 0.f;
+    const int kw = warp * 32;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        uint32_t a[4];
+        ldmatrix_x4(a, smem_u32(Qs + swizzled_offset<HD>((lane & 7) + ((lane >> 3) & 1) * 8,
+                                                        2 * ks + (lane >> 4))));
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+            uint32_t b[4];
+            ldmatrix_x4(b, smem_u32(Ks + tma_tile_offset(kw + np * 16 + (lane & 7) + (lane >> 4) * 8,
+                                                         2 * ks + ((lane >> 3) & 1))));
+            mma_bf16_16816(s[2 * np], a, b[0], b[1]);
+            mma_bf16_16816(s[2 * np + 1], a, b[2], b[3]);
+        }
+    }
+    float m_lo = -INFINITY, m_hi = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int key = k0 + kw + nt * 8 + (lane & 3) * 2 + (e & 1);
+            const bool ok = key < rg.kv_len && key >= rg.first_key;
+            const float v = ok ? s[nt][e] * scale_log2e : -INFINITY;
+            s[nt][e] = v;
+            if (e < 2) m_lo = fmaxf(m_lo, v); else m_hi = fmaxf(m_hi, v);
+        }
+    m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 1));
+    m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2));
+    m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
+    m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2));
+    const float ms_lo = m_lo == -INFINITY ? 0.f : m_lo, ms_hi = m_hi == -INFINITY ? 0.f : m_hi;
+    float l_lo = 0.f, l_hi = 0.f;
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        const uint32_t lo = pack_bf16(exp2f(s[nt][0] - ms_lo), exp2f(s[nt][1] - ms_lo));
+        const uint32_t hi = pack_bf16(exp2f(s[nt][2] - ms_hi), exp2f(s[nt][3] - ms_hi));
+        const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&lo);
+        const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&hi);
+        l_lo += __low2float(lo2) + __high2float(lo2);
+        l_hi += __low2float(hi2) + __high2float(hi2);
+        pa[nt >> 1][(nt & 1) * 2] = lo;
+        pa[nt >> 1][(nt & 1) * 2 + 1] = hi;
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    ok_wait = mbar_wait(bar_v, 0) && ok_wait;
+    if (!ok_wait) {
+        // a copy did not complete within the limit: record it; the values written below are
+        // not to be trusted and the host raises when it reads the error word
+        if (lane == 0) atomicExch(&g_decode_tma_error, 1);
+    }
+    // ---- O = P V
+    float o[HD / 8][4];
+#pragma unroll
+    for (int a = 0; a < HD / 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) o[a][b] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk)
+#pragma unroll
+        for (int dc = 0; dc < HD / 16; ++dc) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, smem_u32(Vs + tma_tile_offset(
+                                     kw + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                     2 * dc + (lane >> 4))));
+            mma_bf16_16816(o[2 * dc], pa[kk], b[0], b[1]);
+            mma_bf16_16816(o[2 * dc + 1], pa[kk], b[2], b[3]);
+        }
+    __syncthreads();       // every warp is done with K: its space takes the warps' outputs
+    float* obuf = reinterpret_cast<float*>(Ks);          // [4][16][HD] floats = TILE bytes
+    {
+        const int r_lo = lane >> 2, r_hi = r_lo + 8;
+        float* ob = obuf + static_cast<size_t>(warp) * kTdRows * HD;
+#pragma unroll
+        for (int nt = 0; nt < HD / 8; ++nt) {
+            const int d = nt * 8 + (lane & 3) * 2;
+            *reinterpret_cast<float2*>(ob + r_lo * HD + d) = make_float2(o[nt][0], o[nt][1]);
+            *reinterpret_cast<float2*>(ob + r_hi * HD + d) = make_float2(o[nt][2], o[nt][3]);
+        }
+        if ((lane & 3) == 0) {
+            m_s[warp][r_lo] = m_lo; l_s[warp][r_lo] = l_lo;
+            m_s[warp][r_hi] = m_hi; l_s[warp][r_hi] = l_hi;
+        }
+    }
+    __syncthreads();
+    const bool single = rg.n_splits - rg.first_split == 1;
+    for (int idx = tid; idx < G * HD; idx += kTdThreads) {
+        const int g = idx / HD, d = idx - g * HD;
+        const float M = fmaxf(fmaxf(m_s[0][g], m_s[1][g]), fmaxf(m_s[2][g], m_s[3][g]));
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float f = m_s[w][g] == -INFINITY ? 0.f : exp2f(m_s[w][g] - M);
+            acc += f * obuf[(w * kTdRows + g) * HD + d];
+            L += f * l_s[w][g];
+        }
+        const int head = kvh * G + g;
+        if (single) {
+            out[static_cast<size_t>(row) * nq * HD + head * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const size_t p = (static_cast<size_t>(i) * nq + head) * max_splits + split;
+            part_o[p * HD + d] = acc;
+            if (d == 0) { part_ml[2 * p] = M; part_ml[2 * p + 1] = L; }
+        }
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(HD)
+paged_decode_tma_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                              int max_splits, const int* __restrict__ ctx_len, int row_base,
+                              int req_base, int nq, int window, __nv_bfloat16* __restrict__ out) {
+    const int i = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    const TdRange rg = td_range(ctx_len[req_base + i], window);
+    if (rg.n_splits - rg.first_split == 1) return;
+    const size_t base = (static_cast<size_t>(i) * nq + head) * max_splits;
+    float M = -INFINITY;
+    for (int s = rg.first_split; s < rg.n_splits; ++s) M = fmaxf(M, part_ml[2 * (base + s)]);
+    float acc = 0.f, L = 0.f;
+    for (int s = rg.first_split; s < rg.n_splits; ++s) {
+        const float f = exp2f(part_ml[2 * (base + s)] - M);
+        acc += f * part_o[(base + s) * HD + d];
+        L += f * part_ml[2 * (base + s) + 1];
+    }
+    out[static_cast<size_t>(row_base + i) * nq * HD + head * HD + d] = __float2bfloat16_rn(acc / L);
+}
+
+template <int HD>
+int launch_tma_decode(const CUtensorMap* map, const void* qkv, int row_stride, int row_base,
+                      int req_base, int n_decode, long long k_row0, long long v_row0,
+                      const int* block_table, int bt_stride, const int* ctx_len, int nq, int nkv,
+                      int page_size, float scale, int window, float* part_o, float* part_ml,
+                      int max_splits, void* out, cudaStream_t stream) {
+    constexpr int TILE = (HD / 64) * kHalfBytes;
+    const size_t smem = 2 * TILE + kTdRows * HD * 2 + 1024;
+    cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)smem);
+    dim3 grid(max_splits, nkv, n_decode);
+    paged_decode_tma_kernel<HD><<<grid, kTdThreads, smem, stream>>>(
+        *map, static_cast<const __nv_bfloat16*>(qkv), row_stride, row_base, req_base, k_row0,
+        v_row0, block_table, bt_stride, ctx_len, nq, nkv, page_size,
+        scale * 1.4426950408889634f, window, part_o, part_ml, max_splits,
+        static_cast<__nv_bfloat16*>(out));
+    int rc = launch_status();
+    if (rc != 0 || max_splits == 1) return rc;
+    dim3 mgrid(n_decode, nq);
+    paged_decode_tma_merge_kernel<HD><<<mgrid, HD, 0, stream>>>(
+        part_o, part_ml, max_splits, ctx_len, row_base, req_base, nq, window,
+        static_cast<__nv_bfloat16*>(out));
+    return launch_status();
+}
+
+}  // namespace somi
+
+using namespace somi;
+
+SOMI_API int somi_decode_tma_supported(int nq, int nkv, int hd, int page_size) {
+    if (nkv <= 0 || nq % nkv || nq / nkv > kTdRows) return 0;
+    if (hd != 64 && hd != 128) return 0;
+    return page_size >= 8 && page_size % 8 == 0 && kTdChunk % page_size == 0;
+}
+
+// Fills `map_out` (128 bytes, 64-byte aligned) for a cache storage of `rows` x `hd` bfloat16.
+SOMI_API int somi_make_kv_tensor_map(void* map_out, const void* storage, long long rows, int hd,
+                                     int page_size) {
+    return make_tensor_map_bf16_2d(static_cast<CUtensorMap*>(map_out), storage,
+                                   static_cast<uint64_t>(rows), static_cast<uint64_t>(hd),
+                                   static_cast<uint32_t>(page_size), 64, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// Reads and clears the error word of the TMA decode kernel (synchronises the device).
+SOMI_API int somi_decode_tma_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_decode_tma_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_decode_tma_error, &zero, sizeof(int));
+    return v;
+}
+
+// k_row0 / v_row0: first row, in the tensor map, of this run's key and value planes.
+SOMI_API int somi_paged_attention_decode_tma(
+    const void* tensor_map, const void* qkv, int row_stride, int row_base, int req_base,
+    int n_decode, long long k_row0, long long v_row0, const int* block_table, int bt_stride,
+    const int* ctx_len, int nq, int nkv, int hd, int page_size, float scale, int window,
+    float* part_o, float* part_ml, int max_splits, void* out, cudaStream_t stream) {
+    if (n_decode <= 0) return 0;
+    if (!somi_decode_tma_supported(nq, nkv, hd, page_size) || max_splits <= 0 ||
+        n_decode > 65535 || nkv > 65535)
+        return SOMI_ERR_UNSUPPORTED;
+    const CUtensorMap* map = static_cast<const CUtensorMap*>(tensor_map);
+    if (hd == 64)
+        return launch_tma_decode<64>(map, qkv, row_stride, row_base, req_base, n_decode, k_row0,
+                                     v_row0, block_table, bt_stride, ctx_len, nq, nkv, page_size,
+                                     scale, window, part_o, part_ml, max_splits, out, stream);
+    return launch_tma_decode<128>(map, qkv, row_stride, row_base, req_base, n_decode, k_row0,
+                                  v_row0, block_table, bt_stride, ctx_len, nq, nkv, page_size,
+                                  scale, window, part_o, part_ml, max_splits, out, stream);
+}

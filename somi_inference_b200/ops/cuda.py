@@ -64,6 +64,8 @@ class CudaOps:
         self.lib.somi_decode_chunk.restype = ctypes.c_int
         self.decode_chunk = int(self.lib.somi_decode_chunk())
         self._workspace = None
+        self._tensor_maps: dict = {}
+        self.use_tma_decode = True
         self._retired: list = []
         self.launches = 0     # kernels of this library launched so far
 
@@ -136,8 +138,30 @@ class CudaOps:
         return dtype == torch.bfloat16 and bool(self.lib.somi_decode_supported(
             ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd)))
 
+    def _kv_tensor_map(self, storage: torch.Tensor, hd: int, page_size: int):
+        """A TMA tensor map over a cache group's whole storage, seen as [rows, hd] bfloat16."""
+        key = (storage.data_ptr(), storage.numel(), hd, page_size)
+        entry = self._tensor_maps.get(key)
+        if entry is None:
+            raw = (ctypes.c_ubyte * 256)()
+            addr = (ctypes.addressof(raw) + 127) & ~127
+            rc = self.lib.somi_make_kv_tensor_map(ctypes.c_void_p(addr), _ptr(storage),
+                                                  ctypes.c_longlong(storage.numel() // hd),
+                                                  ctypes.c_int(hd), ctypes.c_int(page_size))
+            if rc != 0:
+                raise KernelError(f"could not encode a tensor map over the cache (code {rc})")
+            entry = (raw, addr)
+            self._tensor_maps[key] = entry
+        return entry[1]
+
+    def check_errors(self) -> None:
+        """Raise if a kernel recorded that one of its bounded waits ran out (synchronises)."""
+        if int(self.lib.somi_decode_tma_error()) != 0:
+            raise KernelError("the TMA decode attention kernel gave up waiting for a copy; "
+                              "its results are not valid")
+
     def paged_attention(self, qkv, kcache, vcache, batch, group, nq, nkv, hd, scale, window,
-                        out) -> None:
+                        out, storage=None) -> None:
         """Attention of every token of the step over the cache (keys/values already stored).
 
         In bfloat16 with head sizes 32/64/128, portions of prompts go to the tensor-core
@@ -179,14 +203,33 @@ class CudaOps:
             max_splits = -(-group.width * page_size // chunk)
             n_o = n_decode * nq * max_splits * hd
             ws = self._scratch(n_o + n_decode * nq * max_splits * 2, qkv.device)
-            rc = self.lib.somi_paged_attention_decode(
-                _ptr(qkv), ctypes.c_int(qkv.shape[1]), ctypes.c_int(batch.num_prefill_tokens),
-                ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(n_decode), _ptr(kcache),
-                _ptr(vcache), _ptr(group.block_table), ctypes.c_int(group.width),
-                _ptr(batch.ctx_len), ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd),
-                ctypes.c_int(page_size), ctypes.c_float(scale), ctypes.c_int(win),
-                ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(ws.data_ptr() + 4 * n_o),
-                ctypes.c_int(max_splits), _ptr(out), self._stream())
+            tma = (self.use_tma_decode and storage is not None and bool(
+                self.lib.somi_decode_tma_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
+                                                   ctypes.c_int(hd), ctypes.c_int(page_size))))
+            if tma:
+                row_bytes = hd * 2
+                k_row0 = (kcache.data_ptr() - storage.data_ptr()) // row_bytes
+                v_row0 = (vcache.data_ptr() - storage.data_ptr()) // row_bytes
+                rc = self.lib.somi_paged_attention_decode_tma(
+                    ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)), _ptr(qkv),
+                    ctypes.c_int(qkv.shape[1]), ctypes.c_int(batch.num_prefill_tokens),
+                    ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(n_decode),
+                    ctypes.c_longlong(k_row0), ctypes.c_longlong(v_row0),
+                    _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.ctx_len),
+                    ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd),
+                    ctypes.c_int(page_size), ctypes.c_float(scale), ctypes.c_int(win),
+                    ctypes.c_void_p(ws.data_ptr()), ctypes.c_void_p(ws.data_ptr() + 4 * n_o),
+                    ctypes.c_int(max_splits), _ptr(out), self._stream())
+            else:
+                rc = self.lib.somi_paged_attention_decode(
+                    _ptr(qkv), ctypes.c_int(qkv.shape[1]), ctypes.c_int(batch.num_prefill_tokens),
+                    ctypes.c_int(batch.num_prefill_requests), ctypes.c_int(n_decode),
+                    _ptr(kcache), _ptr(vcache), _ptr(group.block_table),
+                    ctypes.c_int(group.width), _ptr(batch.ctx_len), ctypes.c_int(nq),
+                    ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
+                    ctypes.c_float(scale), ctypes.c_int(win), ctypes.c_void_p(ws.data_ptr()),
+                    ctypes.c_void_p(ws.data_ptr() + 4 * n_o), ctypes.c_int(max_splits),
+                    _ptr(out), self._stream())
             self._done(rc, "paged_attention_decode")
             if max_splits > 1:
                 self.launches += 1

@@ -79,5 +79,5 @@ class AttentionMixer:
         self.ctx.ops.paged_attention(qkv, paged.keys, paged.values, batch,
                                      batch.groups[paged.group], self.num_heads,
                                      self.num_kv_heads, self.head_dim, self.scale,
-                                     self.window, out)
+                                     self.window, out, storage=paged.storage)
         return self.out(out)

@@ -55,7 +55,7 @@ class HostOps:
             vcache[page, :, off, :] = x[:, nq + nkv:, :]
 
     def paged_attention(self, qkv, kcache, vcache, batch, group, nq, nkv, hd, scale, window,
-                        out) -> None:
+                        out, storage=None) -> None:
         T = qkv.shape[0]
         q = qkv.view(T, nq + 2 * nkv, hd)[:, :nq].float()
         ps = kcache.shape[2]

@@ -162,8 +162,12 @@ def test_attention_far_key_and_window_edge(ops, dtype, window):
         for h in range(nkv):
             keys[page, h, off] = (q[0, h * (nq // nkv)].float() * 20).to(dtype)
         out = torch.empty(1, nq * hd, dtype=dtype, device="cuda")
-        ops.paged_attention(qkv, keys, view.values, batch, batch.groups[0], nq, nkv, hd,
-                            hd ** -0.5, window, out)
+        store = view.storage.clone()       # the TMA kernel reads through the group's storage
+        ks, vs = store[0, 0], store[0, 1]
+        ks.copy_(keys)
+        ops.paged_attention(qkv, ks, vs, batch, batch.groups[0], nq, nkv, hd,
+                            hd ** -0.5, window, out, storage=store)
+        ops.check_errors()
         got = out.view(nq, hd)[0].float()
         planted = view.values[page, 0, off].float()
         seen = window is None or spot > qpos - window
@@ -182,8 +186,9 @@ DECODE_CASES = [
 ]
 
 
+@pytest.mark.parametrize("tma", [True, False], ids=["tma", "cp_async"])
 @pytest.mark.parametrize("case", DECODE_CASES, ids=[f"d{i}" for i in range(len(DECODE_CASES))])
-def test_split_kv_decode_attention(ops, case):
+def test_split_kv_decode_attention(ops, case, tma):
     """Single-token requests around the 128-key chunk edges, with and without a window, beside
     one prompt portion; bfloat16 goes through the split-KV kernel."""
     nq, nkv, hd, ps, window, ctxs = case
@@ -194,8 +199,13 @@ def test_split_kv_decode_attention(ops, case):
                                               seed=7)
     out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
     before = ops.launches
-    ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
-                        hd ** -0.5, window, out)
+    ops.use_tma_decode = tma
+    try:
+        ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
+                            hd ** -0.5, window, out, storage=view.storage)
+        ops.check_errors()
+    finally:
+        ops.use_tma_decode = True
     assert ops.launches - before >= 2      # one kernel for the portion, the split kernel for the rest
     ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
     cb = batch_to_cpu(batch)
