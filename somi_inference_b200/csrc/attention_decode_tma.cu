@@ -17,7 +17,8 @@
 namespace somi {
 
 constexpr int kTdChunk = 128;
-constexpr int kTdThreads = 128;
+constexpr int kTdThreads = 128;     // 4 warps: 32 keys each for the scores, HD/4 columns each for P.V
+constexpr int kTdWarps = kTdThreads / 32;
 constexpr int kTdRows = 16;
 constexpr int kHalfBytes = kTdChunk * 128;     // one 64-element half of a 128-key tile
 
@@ -41,7 +42,7 @@ __device__ __forceinline__ TdRange td_range(int ctx_len, int window) {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kTdThreads)
+__global__ void __launch_bounds__(kTdThreads, 3)
 paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
                         const __nv_bfloat16* __restrict__ qkv, int row_stride, int row_base,
                         int req_base, long long k_row0, long long v_row0,
@@ -53,14 +54,16 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     constexpr int CPR = HD / 8;
     constexpr int HALVES = HD / 64;
     constexpr int TILE = HALVES * kHalfBytes;
+    constexpr int DW = HD / kTdWarps;             // output columns owned by one warp in P.V
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* Ks = base;                     // HALVES x [128][64] bf16, hardware swizzle
     unsigned char* Vs = Ks + TILE;
     unsigned char* Qs = Vs + TILE;                // [16][HD] bf16, software swizzle
+    unsigned char* Ps = Qs + kTdRows * HD * 2;    // [16][128 keys] bf16, software swizzle
     __shared__ __align__(8) unsigned long long bars[2];
-    __shared__ float m_s[4][kTdRows], l_s[4][kTdRows];
+    __shared__ float m_s[kTdWarps][kTdRows], l_s[kTdWarps][kTdRows];
 
     const int split = blockIdx.x, kvh = blockIdx.y, i = blockIdx.z;
     const int req = req_base + i, row = row_base + i;
@@ -78,10 +81,33 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     const int last_page = (min(k0 + kTdChunk, rg.kv_len) - 1) / page_size;
     const int chunk_page0 = k0 / page_size;
 
-    if (tid == 0) {
-        mbar_init(bar_k, 1);
-        mbar_init(bar_v, 1);
-        mbar_fence_init();
+    // Warp 0 starts the copies before anything else: lane 0 arms both barriers with the byte
+    // counts, then one lane per page looks its page up and issues that page's copies, so the
+    // page-table reads run side by side instead of one after another.
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_init(bar_k, 1);
+            mbar_init(bar_v, 1);
+            mbar_fence_init();
+            const uint32_t bytes = static_cast<uint32_t>(last_page - first_page + 1) * page_size * HD * 2;
+            mbar_expect_tx(bar_k, bytes);
+            mbar_expect_tx(bar_v, bytes);
+        }
+        __syncwarp();
+        for (int p = lane; p < pages_in_chunk; p += 32) {
+            const int ap = chunk_page0 + p;
+            if (ap < first_page || ap > last_page) continue;
+            const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
+            const int r = p * page_size;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_2d(smem_u32(Ks + h * kHalfBytes + r * 128), &kv_map, h * 64,
+                            static_cast<int>(k_row0 + prow), bar_k);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_2d(smem_u32(Vs + h * kHalfBytes + r * 128), &kv_map, h * 64,
+                            static_cast<int>(v_row0 + prow), bar_v);
+        }
     }
     // V rows of pages that are not loaded must not hold stale non-finite bit patterns
     for (int p = 0; p < pages_in_chunk; ++p) {
@@ -96,34 +122,13 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     const __nv_bfloat16* qrow = qkv + static_cast<size_t>(row) * row_stride + static_cast<size_t>(kvh) * G * HD;
     for (int c = tid; c < kTdRows * CPR; c += kTdThreads) {
         const int r = c / CPR, ch = c - r * CPR;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < G) v = *reinterpret_cast<const uint4*>(qrow + r * HD + ch * 8);
-        *reinterpret_cast<uint4*>(Qs + swizzled_offset<HD>(r, ch)) = v;
+        const bool ok = r < G;
+        cp_async_16(smem_u32(Qs + swizzled_offset<HD>(r, ch)), ok ? qrow + r * HD + ch * 8 : qrow,
+                    ok ? 16 : 0);
     }
-    fence_proxy_async();        // the zero fill above is ordered before the async proxy's writes
-    __syncthreads();
-
-    if (tid == 0) {
-        const uint32_t bytes = static_cast<uint32_t>(last_page - first_page + 1) * page_size * HD * 2;
-        mbar_expect_tx(bar_k, bytes);
-        for (int ap = first_page; ap <= last_page; ++ap) {
-            const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
-            const int r = (ap - chunk_page0) * page_size;
-#pragma unroll
-            for (int h = 0; h < HALVES; ++h)
-                tma_load_2d(smem_u32(Ks + h * kHalfBytes + r * 128), &kv_map, h * 64,
-                            static_cast<int>(k_row0 + prow), bar_k);
-        }
-        mbar_expect_tx(bar_v, bytes);
-        for (int ap = first_page; ap <= last_page; ++ap) {
-            const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
-            const int r = (ap - chunk_page0) * page_size;
-#pragma unroll
-            for (int h = 0; h < HALVES; ++h)
-                tma_load_2d(smem_u32(Vs + h * kHalfBytes + r * 128), &kv_map, h * 64,
-                            static_cast<int>(v_row0 + prow), bar_v);
-        }
-    }
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();      // Q is in place; the barriers' initialisation is visible to all warps
 
     bool ok_wait = mbar_wait(bar_k, 0);
     // ---- S = Q K^T for this warp's 32 keys
@@ -147,6 +152,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
             mma_bf16_16816(s[2 * np + 1], a, b[2], b[3]);
         }
     }
+    // ---- mask; the row maximum is taken over the whole chunk (all four warps)
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
     float m_lo = -INFINITY, m_hi = -INFINITY;
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt)
@@ -162,24 +169,31 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     m_lo = fmaxf(m_lo, __shfl_xor_sync(0xffffffffu, m_lo, 2));
     m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 1));
     m_hi = fmaxf(m_hi, __shfl_xor_sync(0xffffffffu, m_hi, 2));
-    const float ms_lo = m_lo == -INFINITY ? 0.f : m_lo, ms_hi = m_hi == -INFINITY ? 0.f : m_hi;
+    if ((lane & 3) == 0) { m_s[warp][r_lo] = m_lo; m_s[warp][r_hi] = m_hi; }
+    __syncthreads();
+    float M_lo = fmaxf(fmaxf(m_s[0][r_lo], m_s[1][r_lo]), fmaxf(m_s[2][r_lo], m_s[3][r_lo]));
+    float M_hi = fmaxf(fmaxf(m_s[0][r_hi], m_s[1][r_hi]), fmaxf(m_s[2][r_hi], m_s[3][r_hi]));
+    // a valid chunk has at least one visible key, so the maxima of real rows are finite
+    const float b_lo = M_lo == -INFINITY ? 0.f : M_lo, b_hi = M_hi == -INFINITY ? 0.f : M_hi;
     float l_lo = 0.f, l_hi = 0.f;
-    uint32_t pa[2][4];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
-        const uint32_t lo = pack_bf16(exp2f(s[nt][0] - ms_lo), exp2f(s[nt][1] - ms_lo));
-        const uint32_t hi = pack_bf16(exp2f(s[nt][2] - ms_hi), exp2f(s[nt][3] - ms_hi));
+        const uint32_t lo = pack_bf16(fast_exp2(s[nt][0] - b_lo), fast_exp2(s[nt][1] - b_lo));
+        const uint32_t hi = pack_bf16(fast_exp2(s[nt][2] - b_hi), fast_exp2(s[nt][3] - b_hi));
         const __nv_bfloat162 lo2 = *reinterpret_cast<const __nv_bfloat162*>(&lo);
         const __nv_bfloat162 hi2 = *reinterpret_cast<const __nv_bfloat162*>(&hi);
         l_lo += __low2float(lo2) + __high2float(lo2);
         l_hi += __low2float(hi2) + __high2float(hi2);
-        pa[nt >> 1][(nt & 1) * 2] = lo;
-        pa[nt >> 1][(nt & 1) * 2 + 1] = hi;
+        // P goes to shared memory: every warp needs all 128 keys of it for its output columns
+        const int chunk = warp * 4 + nt;
+        *reinterpret_cast<uint32_t*>(Ps + swizzled_offset<128>(r_lo, chunk) + (lane & 3) * 4) = lo;
+        *reinterpret_cast<uint32_t*>(Ps + swizzled_offset<128>(r_hi, chunk) + (lane & 3) * 4) = hi;
     }
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if ((lane & 3) == 0) { l_s[warp][r_lo] = l_lo; l_s[warp][r_hi] = l_hi; }
 
     ok_wait = mbar_wait(bar_v, 0) && ok_wait;
     if (!ok_wait) {
@@ -187,58 +201,54 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
         // not to be trusted and the host raises when it reads the error word
         if (lane == 0) atomicExch(&g_decode_tma_error, 1);
     }
-    // ---- O = P V
-    float o[HD / 8][4];
+    __syncthreads();       // P and the row sums of all warps are in shared memory
+
+    // ---- O[:, warp's DW columns] = P V over all 128 keys: no reduction across warps
+    float o[DW / 8][4];
 #pragma unroll
-    for (int a = 0; a < HD / 8; ++a)
+    for (int a = 0; a < DW / 8; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b) o[a][b] = 0.f;
+    const int c0 = warp * (DW / 8);               // first 16-byte chunk of this warp's columns
 #pragma unroll
-    for (int kk = 0; kk < 2; ++kk)
+    for (int kk = 0; kk < kTdChunk / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, smem_u32(Ps + swizzled_offset<128>((lane & 7) + ((lane >> 3) & 1) * 8,
+                                                         2 * kk + (lane >> 4))));
 #pragma unroll
-        for (int dc = 0; dc < HD / 16; ++dc) {
+        for (int dc = 0; dc < DW / 16; ++dc) {
             uint32_t b[4];
             ldmatrix_x4_trans(b, smem_u32(Vs + tma_tile_offset(
-                                     kw + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
-                                     2 * dc + (lane >> 4))));
-            mma_bf16_16816(o[2 * dc], pa[kk], b[0], b[1]);
-            mma_bf16_16816(o[2 * dc + 1], pa[kk], b[2], b[3]);
-        }
-    __syncthreads();       // every warp is done with K: its space takes the warps' outputs
-    float* obuf = reinterpret_cast<float*>(Ks);          // [4][16][HD] floats = TILE bytes
-    {
-        const int r_lo = lane >> 2, r_hi = r_lo + 8;
-        float* ob = obuf + static_cast<size_t>(warp) * kTdRows * HD;
-#pragma unroll
-        for (int nt = 0; nt < HD / 8; ++nt) {
-            const int d = nt * 8 + (lane & 3) * 2;
-            *reinterpret_cast<float2*>(ob + r_lo * HD + d) = make_float2(o[nt][0], o[nt][1]);
-            *reinterpret_cast<float2*>(ob + r_hi * HD + d) = make_float2(o[nt][2], o[nt][3]);
-        }
-        if ((lane & 3) == 0) {
-            m_s[warp][r_lo] = m_lo; l_s[warp][r_lo] = l_lo;
-            m_s[warp][r_hi] = m_hi; l_s[warp][r_hi] = l_hi;
+                                     kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
+                                     c0 + 2 * dc + (lane >> 4))));
+            mma_bf16_16816(o[2 * dc], a, b[0], b[1]);
+            mma_bf16_16816(o[2 * dc + 1], a, b[2], b[3]);
         }
     }
-    __syncthreads();
+    const float L_lo = l_s[0][r_lo] + l_s[1][r_lo] + l_s[2][r_lo] + l_s[3][r_lo];
+    const float L_hi = l_s[0][r_hi] + l_s[1][r_hi] + l_s[2][r_hi] + l_s[3][r_hi];
     const bool single = rg.n_splits - rg.first_split == 1;
-    for (int idx = tid; idx < G * HD; idx += kTdThreads) {
-        const int g = idx / HD, d = idx - g * HD;
-        const float M = fmaxf(fmaxf(m_s[0][g], m_s[1][g]), fmaxf(m_s[2][g], m_s[3][g]));
-        float acc = 0.f, L = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float f = m_s[w][g] == -INFINITY ? 0.f : exp2f(m_s[w][g] - M);
-            acc += f * obuf[(w * kTdRows + g) * HD + d];
-            L += f * l_s[w][g];
-        }
+    for (int half = 0; half < 2; ++half) {
+        const int g = half ? r_hi : r_lo;
+        if (g >= G) continue;
         const int head = kvh * G + g;
+        const float L = half ? L_hi : L_lo, M = half ? M_hi : M_lo;
         if (single) {
-            out[static_cast<size_t>(row) * nq * HD + head * HD + d] = __float2bfloat16_rn(acc / L);
+            const float inv = 1.0f / L;
+            __nv_bfloat16* dst = out + static_cast<size_t>(row) * nq * HD + head * HD + warp * DW;
+#pragma unroll
+            for (int nt = 0; nt < DW / 8; ++nt)
+                *reinterpret_cast<uint32_t*>(dst + nt * 8 + (lane & 3) * 2) =
+                    pack_bf16(o[nt][half * 2] * inv, o[nt][half * 2 + 1] * inv);
         } else {
             const size_t p = (static_cast<size_t>(i) * nq + head) * max_splits + split;
-            part_o[p * HD + d] = acc;
-            if (d == 0) { part_ml[2 * p] = M; part_ml[2 * p + 1] = L; }
+            float* dst = part_o + p * HD + warp * DW;
+#pragma unroll
+            for (int nt = 0; nt < DW / 8; ++nt)
+                *reinterpret_cast<float2*>(dst + nt * 8 + (lane & 3) * 2) =
+                    make_float2(o[nt][half * 2], o[nt][half * 2 + 1]);
+            if (warp == 0 && (lane & 3) == 0) { part_ml[2 * p] = M; part_ml[2 * p + 1] = L; }
         }
     }
 }
@@ -270,7 +280,7 @@ int launch_tma_decode(const CUtensorMap* map, const void* qkv, int row_stride, i
                       int page_size, float scale, int window, float* part_o, float* part_ml,
                       int max_splits, void* out, cudaStream_t stream) {
     constexpr int TILE = (HD / 64) * kHalfBytes;
-    const size_t smem = 2 * TILE + kTdRows * HD * 2 + 1024;
+    const size_t smem = 2 * TILE + kTdRows * HD * 2 + kTdRows * kTdChunk * 2 + 1024;
     cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
     dim3 grid(max_splits, nkv, n_decode);
