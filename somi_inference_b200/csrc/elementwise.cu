@@ -5,6 +5,49 @@
 
 namespace somi {
 
+// Four consecutive elements at once (16 bytes of float32, 8 bytes of bfloat16).
+struct F4 { float v[4]; };
+__device__ __forceinline__ F4 load4(const float* p) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    return F4{{t.x, t.y, t.z, t.w}};
+}
+__device__ __forceinline__ F4 load4(const __nv_bfloat16* p) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+    return F4{{__low2float(a), __high2float(a), __low2float(b), __high2float(b)}};
+}
+__device__ __forceinline__ void store4(float* p, const F4& f) {
+    *reinterpret_cast<float4*>(p) = make_float4(f.v[0], f.v[1], f.v[2], f.v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const F4& f) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(f.v[0], f.v[1]);
+    __nv_bfloat162 b = __floats2bfloat162_rn(f.v[2], f.v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<uint32_t*>(&a);
+    t.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+struct F2 { float x, y; };
+__device__ __forceinline__ F2 load2(const float* p) {
+    const float2 t = *reinterpret_cast<const float2*>(p);
+    return F2{t.x, t.y};
+}
+__device__ __forceinline__ F2 load2(const __nv_bfloat16* p) {
+    const __nv_bfloat162 t = *reinterpret_cast<const __nv_bfloat162*>(p);
+    return F2{__low2float(t), __high2float(t)};
+}
+__device__ __forceinline__ void store2(float* p, float x, float y) {
+    *reinterpret_cast<float2*>(p) = make_float2(x, y);
+}
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float x, float y) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(x, y);
+}
+__device__ __forceinline__ F4 load4_any(const void* p, int dtype, size_t i) {
+    return dtype == SOMI_F32 ? load4(reinterpret_cast<const float*>(p) + i)
+                             : load4(reinterpret_cast<const __nv_bfloat16*>(p) + i);
+}
+
 // ---------------------------------------------------------------- embedding
 // out[t, :] = float(table[ids[t], :])
 template <typename T>
@@ -13,6 +56,10 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
     const int t = blockIdx.x;
     const T* row = table + static_cast<size_t>(ids[t]) * H;
     float* o = out + static_cast<size_t>(t) * H;
+    if ((H & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) store4(o + i, load4(row + i));
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
 }
 
@@ -25,13 +72,38 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    const void* __restrict__ weight, int weight_dtype, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int H,
                                    int write_back) {
-    extern __shared__ float row_buf[];
+    extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
     const int b = blockIdx.x;
     const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
     float* r = residual + row * H;
     const TD* d = delta ? delta + row * H : nullptr;
     float ss = 0.f;
+    TO* o = out + static_cast<size_t>(b) * H;
+    if ((H & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            F4 v = load4(r + i);
+            if (d) {
+                const F4 dv = load4(d + i);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v.v[k] += dv.v[k];
+                if (write_back) store4(r + i, v);
+            }
+            store4(row_buf + i, v);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ss += v.v[k] * v.v[k];
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            F4 v = load4(row_buf + i);
+            const F4 w = load4_any(weight, weight_dtype, i);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v.v[k] = v.v[k] * inv * w.v[k];
+            store4(o + i, v);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = r[i];
         if (d) v += to_float(d[i]);
@@ -41,7 +113,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
-    TO* o = out + static_cast<size_t>(b) * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x)
         o[i] = from_float<TO>(row_buf[i] * inv * load_as_float(weight, weight_dtype, i));
 }
@@ -71,20 +142,39 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     const int slot = slot_map ? slot_map[t] : -1;
     const int page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? slot % page_size : 0;
-    // queries and keys: rotated pairs
-    for (int idx = threadIdx.x; idx < (nq + nkv) * half; idx += blockDim.x) {
-        const int head = idx / half, i = idx - head * half;
-        T* x = row + static_cast<size_t>(head) * hd;
-        const float a = to_float(x[i]), b = to_float(x[i + half]);
-        const float c = cs[i], s = cs[half + i];
-        const T o1 = from_float<T>(a * c - b * s);
-        const T o2 = from_float<T>(b * c + a * s);
-        x[i] = o1;
-        x[i + half] = o2;
-        if (slot >= 0 && head >= nq) {
-            T* kc = kcache + ((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd;
-            kc[i] = o1;
-            kc[i + half] = o2;
+    // queries and keys: rotated pairs (two neighbouring pairs per thread where sizes allow)
+    if ((half & 1) == 0 && (hd & 1) == 0) {
+        const int hp = half >> 1;
+        for (int idx = threadIdx.x; idx < (nq + nkv) * hp; idx += blockDim.x) {
+            const int head = idx / hp, i = (idx - head * hp) << 1;
+            T* x = row + static_cast<size_t>(head) * hd;
+            const F2 a = load2(x + i), b = load2(x + i + half);
+            const float c0 = cs[i], c1 = cs[i + 1], s0 = cs[half + i], s1 = cs[half + i + 1];
+            const float o1x = a.x * c0 - b.x * s0, o1y = a.y * c1 - b.y * s1;
+            const float o2x = b.x * c0 + a.x * s0, o2y = b.y * c1 + a.y * s1;
+            store2(x + i, o1x, o1y);
+            store2(x + i + half, o2x, o2y);
+            if (slot >= 0 && head >= nq) {
+                T* kc = kcache + ((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd;
+                store2(kc + i, o1x, o1y);
+                store2(kc + i + half, o2x, o2y);
+            }
+        }
+    } else {
+        for (int idx = threadIdx.x; idx < (nq + nkv) * half; idx += blockDim.x) {
+            const int head = idx / half, i = idx - head * half;
+            T* x = row + static_cast<size_t>(head) * hd;
+            const float a = to_float(x[i]), b = to_float(x[i + half]);
+            const float c = cs[i], s = cs[half + i];
+            const T o1 = from_float<T>(a * c - b * s);
+            const T o2 = from_float<T>(b * c + a * s);
+            x[i] = o1;
+            x[i + half] = o2;
+            if (slot >= 0 && head >= nq) {
+                T* kc = kcache + ((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd;
+                kc[i] = o1;
+                kc[i + half] = o2;
+            }
         }
     }
     if (slot < 0) return;
@@ -96,6 +186,15 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
             row[static_cast<size_t>(nq + head) * hd + i];
     }
     const T* v = row + static_cast<size_t>(nq + nkv) * hd;
+    if ((hd & 3) == 0) {
+        const int q4 = hd >> 2;
+        for (int idx = threadIdx.x; idx < nkv * q4; idx += blockDim.x) {
+            const int head = idx / q4, i = (idx - head * q4) << 2;
+            store4(vcache + ((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i,
+                   load4(v + head * hd + i));
+        }
+        return;
+    }
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
         const int head = idx / hd, i = idx - head * hd;
         vcache[((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i] = v[idx];
@@ -106,6 +205,20 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i],  silu(z) = z / (1 + exp(-z))
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {
+    if ((I & 3) == 0) {
+        const size_t n4 = n >> 2;
+        const int I4 = I >> 2;
+        for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < n4;
+             idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+            const size_t t = idx / I4, i = (idx - t * I4) << 2;
+            const F4 g = load4(gu + t * 2 * I + i), u = load4(gu + t * 2 * I + I + i);
+            F4 r;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) r.v[k] = g.v[k] / (1.0f + expf(-g.v[k])) * u.v[k];
+            store4(out + t * I + i, r);
+        }
+        return;
+    }
     for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < n;
          idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t t = idx / I, i = idx - t * I;
@@ -138,7 +251,7 @@ SOMI_API int somi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     if (n_out <= 0) return 0;
     const size_t smem = static_cast<size_t>(H) * sizeof(float);
     if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
 #define SOMI_LAUNCH_NORM(TD, TO)                                                                 \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
@@ -178,7 +291,8 @@ SOMI_API int somi_silu_mul(const void* gu, void* out, int dtype, long long T, in
     const size_t n = static_cast<size_t>(T) * I;
     if (n == 0) return 0;
     const int threads = 256;
-    const int blocks = static_cast<int>(n / threads + 1 < 148 * 16 ? n / threads + 1 : 148 * 16);
+    const size_t work = (I & 3) == 0 ? n / 4 : n;
+    const int blocks = static_cast<int>(work / threads + 1 < 148 * 16 ? work / threads + 1 : 148 * 16);
     if (dtype == SOMI_F32)
         silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(
             static_cast<const float*>(gu), static_cast<float*>(out), I, n);
