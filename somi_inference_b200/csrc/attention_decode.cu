@@ -292,3 +292,92 @@ SOMI_API int somi_paged_attention_decode(
     SOMI_DEC(128);
 #undef SOMI_DEC
 }
+
+// ------------------------------------------------------------------------------------------
+// The same split-KV decode attention for callers that cannot allocate device memory.
+// Declared in attention_decode_static.h; it has no counterpart in the reference.
+//
+// Some hosts of this library may not call cudaMalloc at the moment they need attention: a
+// serving process that gave the whole device to its own pool at start-up, a caller inside a
+// latency-critical loop where an allocation would synchronise the device, or one that simply
+// has no allocator handle to give us.  For them the per-chunk partial results live in a
+// file-scope device array of fixed size instead of caller-provided scratch.  Every GPU that
+// loads the library holds these kStaticScratchFloats * 4 bytes (8 MiB) until the process exits.
+//
+// In host code the array's name is only a host-side stand-in for the device symbol, not a
+// device address, so the address is asked for once per device with cudaGetSymbolAddress (with
+// that device current) and that pointer is what the kernels get.
+namespace somi {
+
+constexpr size_t kStaticScratchFloats = size_t(2) << 20;           // 2 Mi floats = 8 MiB
+constexpr int kStaticMaxDevices = 64;
+static __device__ __align__(256) float g_static_decode_scratch[kStaticScratchFloats];
+static float* g_static_scratch_ptr[kStaticMaxDevices] = {};        // host: device address per GPU
+
+// Returns the device address of the static scratch on the current device (nullptr on failure);
+// the first call on a device asks the runtime for it.
+static float* static_scratch_on_current_device(int* status) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices) {
+        *status = e != cudaSuccess ? static_cast<int>(e) : SOMI_ERR_UNSUPPORTED;
+        return nullptr;
+    }
+    float* p = __atomic_load_n(&g_static_scratch_ptr[dev], __ATOMIC_ACQUIRE);
+    if (p == nullptr) {
+        void* addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_decode_scratch);
+        if (e != cudaSuccess || addr == nullptr) {
+            *status = e != cudaSuccess ? static_cast<int>(e) : SOMI_ERR_UNSUPPORTED;
+            return nullptr;
+        }
+        p = static_cast<float*>(addr);
+        __atomic_store_n(&g_static_scratch_ptr[dev], p, __ATOMIC_RELEASE);
+    }
+    *status = 0;
+    return p;
+}
+
+}  // namespace somi
+
+SOMI_API long long somi_paged_attention_decode_static_capacity() {
+    return static_cast<long long>(kStaticScratchFloats);
+}
+
+SOMI_API const char* somi_paged_attention_decode_static_strerror(int code) {
+    switch (code) {
+        case 0: return "success";
+        case SOMI_ERR_UNSUPPORTED:
+            return "sizes not supported by the split-KV decode attention kernel";
+        case SOMI_ERR_SCRATCH_TOO_SMALL:
+            return "n_decode * num_heads * max_splits * (head_dim + 2) exceeds the static scratch "
+                   "of 2 Mi floats; use somi_paged_attention_decode with caller-provided scratch";
+        default: return "CUDA runtime error (the value is the cudaError_t)";
+    }
+}
+
+SOMI_API int somi_paged_attention_decode_static(
+    const void* qkv, int row_stride, int row_base, int req_base, int n_decode, const void* kcache,
+    const void* vcache, const int* block_table, int bt_stride, const int* ctx_len, int nq, int nkv,
+    int hd, int page_size, float scale, int window, int max_splits, void* out,
+    cudaStream_t stream) {
+    if (n_decode <= 0) return 0;
+    if (!somi_decode_supported(nq, nkv, hd) || page_size <= 0 || max_splits <= 0 ||
+        n_decode > 65535 || nkv > 65535)
+        return SOMI_ERR_UNSUPPORTED;
+    const size_t slots = static_cast<size_t>(n_decode) * nq * max_splits;
+    if (slots > kStaticScratchFloats / (static_cast<size_t>(hd) + 2))
+        return SOMI_ERR_SCRATCH_TOO_SMALL;
+    int status = 0;
+    float* scratch = static_scratch_on_current_device(&status);
+    if (scratch == nullptr) return status;
+    // Layout inside the array: partial outputs first, then (maximum, sum) pairs.  Nothing here
+    // has to start at zero: every slot that the merge kernel reads is written by the split
+    // kernel of the same call, and slots of chunks a request does not have are never read.
+    float* part_o = scratch;
+    float* part_ml = scratch + slots * hd;
+    return somi_paged_attention_decode(qkv, row_stride, row_base, req_base, n_decode, kcache,
+                                       vcache, block_table, bt_stride, ctx_len, nq, nkv, hd,
+                                       page_size, scale, window, part_o, part_ml, max_splits, out,
+                                       stream);
+}

@@ -14,6 +14,7 @@
 #define SOMI_F32 0
 #define SOMI_BF16 1
 #define SOMI_ERR_UNSUPPORTED 10001   // outside every cudaError_t value in use
+#define SOMI_ERR_SCRATCH_TOO_SMALL 10002
 
 #define SOMI_API extern "C" __attribute__((visibility("default")))
 
