@@ -66,6 +66,9 @@ class CudaOps:
         self._workspace = None
         self._tensor_maps: dict = {}
         self.use_tma_decode = True
+        self._gemm_maps: dict = {}
+        self.use_skinny_gemm = True
+        self.skinny_max_tokens = int(self.lib.somi_skinny_gemm_max_tokens())
         self._retired: list = []
         self.launches = 0     # kernels of this library launched so far
 
@@ -159,6 +162,9 @@ class CudaOps:
         if int(self.lib.somi_decode_tma_error()) != 0:
             raise KernelError("the TMA decode attention kernel gave up waiting for a copy; "
                               "its results are not valid")
+        if int(self.lib.somi_gemm_error()) != 0:
+            raise KernelError("the tcgen05 matrix product gave up waiting on a barrier; "
+                              "its results are not valid")
 
     def paged_attention(self, qkv, kcache, vcache, batch, group, nq, nkv, hd, scale, window,
                         out, storage=None) -> None:
@@ -239,6 +245,62 @@ class CudaOps:
         rc = self.lib.somi_silu_mul(_ptr(gu), _ptr(out), _code(gu), ctypes.c_longlong(gu.shape[0]),
                                     ctypes.c_int(out.shape[1]), self._stream())
         self._done(rc, "silu_mul")
+
+    # ------------------------------------------------------- tcgen05 matrix product
+    GEMM_BF16, GEMM_F32, GEMM_PARTIAL_F32, GEMM_SWIGLU = 0, 1, 2, 3
+
+    def skinny_supported(self, M: int, N: int, K: int, dtype) -> bool:
+        """Whether the tensor-memory kernel takes x[M, K] @ w[N, K]^T (few tokens, bfloat16)."""
+        return (self.use_skinny_gemm and dtype == torch.bfloat16 and 1 <= M <= self.skinny_max_tokens
+                and K % 8 == 0 and N >= 1)
+
+    def _gemm_map(self, t: torch.Tensor, box_rows: int) -> int:
+        key = (t.data_ptr(), t.shape[0], t.shape[1], box_rows)
+        entry = self._gemm_maps.get(key)
+        if entry is None:
+            if len(self._gemm_maps) > 8192:
+                self._gemm_maps.clear()
+            raw = (ctypes.c_ubyte * 256)()
+            addr = (ctypes.addressof(raw) + 127) & ~127
+            rc = self.lib.somi_make_gemm_tensor_map(ctypes.c_void_p(addr), _ptr(t),
+                                                    ctypes.c_longlong(t.shape[0]),
+                                                    ctypes.c_longlong(t.shape[1]),
+                                                    ctypes.c_int(box_rows))
+            if rc != 0:
+                raise KernelError(f"could not encode a tensor map over a {tuple(t.shape)} matrix (code {rc})")
+            entry = (raw, addr)
+            self._gemm_maps[key] = entry
+        return entry[1]
+
+    def skinny_gemm(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
+                    mode: int = 0, splits: int = 1) -> torch.Tensor:
+        """x[M, K] @ w[N, K]^T on tcgen05 tensor cores for M <= 64.
+
+        mode GEMM_BF16 -> bf16 [M, N] (+ bias); GEMM_F32 -> float32 [M, N];
+        GEMM_PARTIAL_F32 -> float32 [splits', M, N] partial sums over ranges of K (bias in the
+        first); GEMM_SWIGLU -> bf16 [M, N / 2] = silu(even rows) * odd rows of w.
+        """
+        _check(x, w, bias)
+        M, K = x.shape
+        N = w.shape[0]
+        assert w.shape[1] == K and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+        box = 16 if M <= 16 else (32 if M <= 32 else 64)
+        if mode == self.GEMM_PARTIAL_F32:
+            splits = int(self.lib.somi_skinny_gemm_splits(ctypes.c_int(K), ctypes.c_int(splits)))
+            out = torch.empty((splits, M, N), dtype=torch.float32, device=x.device)
+        elif mode == self.GEMM_F32:
+            out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        elif mode == self.GEMM_SWIGLU:
+            out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        else:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        rc = self.lib.somi_skinny_gemm(
+            ctypes.c_void_p(self._gemm_map(w, 128)), ctypes.c_void_p(self._gemm_map(x, box)),
+            ctypes.c_int(box), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+            ctypes.c_int(splits), ctypes.c_int(mode), _ptr(bias),
+            _code(bias) if bias is not None else _F32, _ptr(out), self._stream())
+        self._done(rc, "skinny_gemm")
+        return out
 
     def sample(self, logits, temperature, top_k, top_p, penalty, seed, counter, hist_off,
                hist_tok, out) -> None:

@@ -1,0 +1,62 @@
+"""The tcgen05/TMA matrix product for few tokens against a float32 product of the same
+bfloat16 inputs, at the engine's sizes and at sizes that are no multiple of any tile."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from somi_inference_b200.ops import cuda_ops
+    return cuda_ops()
+
+
+SHAPES = [(896, 896), (1152, 896), (896, 4864), (3584, 3584), (5000, 3584), (136, 200),
+          (64, 64), (151936 // 8, 896)]
+
+
+@pytest.mark.parametrize("M", [1, 8, 16, 17, 33, 64])
+@pytest.mark.parametrize("N,K", SHAPES)
+def test_skinny_gemm_bf16_and_f32(ops, M, N, K):
+    g = torch.Generator().manual_seed(N + K + M)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
+    ref = x.float() @ w.float().T
+    y32 = ops.skinny_gemm(x, w, None, ops.GEMM_F32)
+    ops.check_errors()
+    scale = ref.abs().max().item()
+    assert (y32 - ref).abs().max().item() <= 2e-5 * max(scale, 1.0) * (K / 64) ** 0.5
+    y = ops.skinny_gemm(x, w, b, ops.GEMM_BF16)
+    torch.testing.assert_close(y.float(), (ref + b.float()).to(torch.bfloat16).float(),
+                               rtol=1.6e-2, atol=1e-2 * max(scale, 1.0))
+
+
+@pytest.mark.parametrize("M,N,K,splits", [(8, 896, 4864, 8), (64, 3584, 18944, 5), (3, 136, 200, 4),
+                                          (16, 1152, 896, 3), (1, 896, 896, 16)])
+def test_skinny_gemm_split_k(ops, M, N, K, splits):
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=g).float().cuda()
+    parts = ops.skinny_gemm(x, w, b, ops.GEMM_PARTIAL_F32, splits=splits)
+    ops.check_errors()
+    assert 1 <= parts.shape[0] <= splits
+    ref = x.float() @ w.float().T + b
+    assert (parts.sum(0) - ref).abs().max().item() <= 1e-4 * max(ref.abs().max().item(), 1.0)
+
+
+@pytest.mark.parametrize("M,I,K", [(8, 4864, 896), (64, 18944, 3584), (5, 88, 80)])
+def test_skinny_gemm_swiglu(ops, M, I, K):
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    gate = (torch.randn(I, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    up = (torch.randn(I, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()     # rows g0, u0, g1, u1, ...
+    y = ops.skinny_gemm(x, w, None, ops.GEMM_SWIGLU)
+    ops.check_errors()
+    gg, uu = x.float() @ gate.float().T, x.float() @ up.float().T
+    ref = gg * torch.sigmoid(gg) * uu
+    torch.testing.assert_close(y.float(), ref, rtol=1.6e-2, atol=1e-2 * max(ref.abs().max().item(), 1.0))
