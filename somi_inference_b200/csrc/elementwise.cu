@@ -67,8 +67,11 @@ __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ 
 // r = residual[row] (+ delta[row]); if write_back: residual[row] = r;
 // out[b] = r / sqrt(mean(r^2) + eps) * weight, where row = rows ? rows[b] : b.
 // The row is kept in shared memory (H floats) between the two passes.
+// `delta` may be `splits` partial sums (float32 only) that lie `split_stride` elements apart; they
+// are added in order, so the result does not depend on how the producer was scheduled.
 template <typename TD, typename TO>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                   int splits, long long split_stride,
                                    const void* __restrict__ weight, int weight_dtype, float eps,
                                    TO* __restrict__ out, const int* __restrict__ rows, int H,
                                    int write_back) {
@@ -84,9 +87,12 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
             F4 v = load4(r + i);
             if (d) {
-                const F4 dv = load4(d + i);
+#pragma unroll 4
+                for (int sp = 0; sp < splits; ++sp) {
+                    const F4 dv = load4(d + sp * split_stride + i);
 #pragma unroll
-                for (int k = 0; k < 4; ++k) v.v[k] += dv.v[k];
+                    for (int k = 0; k < 4; ++k) v.v[k] += dv.v[k];
+                }
                 if (write_back) store4(r + i, v);
             }
             store4(row_buf + i, v);
@@ -106,7 +112,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = r[i];
-        if (d) v += to_float(d[i]);
+        if (d)
+            for (int sp = 0; sp < splits; ++sp) v += to_float(d[sp * split_stride + i]);
         if (write_back && d) r[i] = v;
         row_buf[i] = v;
         ss += v * v;
@@ -201,17 +208,137 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     }
 }
 
+// The same, reading the projection as `splits` float32 partial sums [splits][T][(nq+2nkv)*hd]
+// (what a split-K product leaves) plus a bias: sums them in order, rotates, writes the queries
+// to `q_out` rows (bfloat16, same row layout as qkv) and keys/values to the cache only.
+__global__ void rope_store_partial_kernel(const float* __restrict__ parts, int splits,
+                                          long long split_stride, const void* __restrict__ bias,
+                                          int bias_dtype, __nv_bfloat16* __restrict__ q_out,
+                                          const int* __restrict__ positions,
+                                          const float* __restrict__ inv_freq, int nq, int nkv,
+                                          int hd, int rot, const int* __restrict__ slot_map,
+                                          __nv_bfloat16* __restrict__ kcache,
+                                          __nv_bfloat16* __restrict__ vcache, int page_size) {
+    extern __shared__ float cs[];
+    const int t = blockIdx.x;
+    const int half = rot >> 1;
+    const int width = (nq + 2 * nkv) * hd;
+    const float pos = static_cast<float>(positions[t]);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float s, c;
+        sincosf(pos * inv_freq[i], &s, &c);
+        cs[i] = c;
+        cs[half + i] = s;
+    }
+    __syncthreads();
+    const float* prow = parts + static_cast<size_t>(t) * width;
+    auto value = [&](int col) {
+        float v = bias ? load_as_float(bias, bias_dtype, col) : 0.f;
+        for (int sp = 0; sp < splits; ++sp) v += prow[sp * split_stride + col];
+        return v;
+    };
+    auto value4 = [&](int col) {          // four consecutive columns
+        F4 v = bias ? load4_any(bias, bias_dtype, col) : F4{{0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 4
+        for (int sp = 0; sp < splits; ++sp) {
+            const F4 p = load4(prow + sp * split_stride + col);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v.v[k] += p.v[k];
+        }
+        return v;
+    };
+    __nv_bfloat16* qrow = q_out + static_cast<size_t>(t) * width;
+    const int slot = slot_map ? slot_map[t] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0;
+    const int off = slot >= 0 ? slot % page_size : 0;
+    const int heads = slot >= 0 ? nq + nkv : nq;         // keys matter only if they are stored
+    if ((half & 3) == 0 && (hd & 3) == 0) {
+        const int hq = half >> 2;
+        for (int idx = threadIdx.x; idx < heads * hq; idx += blockDim.x) {
+            const int head = idx / hq, i = (idx - head * hq) << 2;
+            const F4 a = value4(head * hd + i), b = value4(head * hd + i + half);
+            F4 o1, o2;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float c = cs[i + k], s = cs[half + i + k];
+                o1.v[k] = a.v[k] * c - b.v[k] * s;
+                o2.v[k] = b.v[k] * c + a.v[k] * s;
+            }
+            __nv_bfloat16* dst = head < nq
+                ? qrow + head * hd
+                : kcache + ((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd;
+            store4(dst + i, o1);
+            store4(dst + i + half, o2);
+        }
+        const int tail4 = (hd - rot) >> 2;
+        for (int idx = threadIdx.x; idx < heads * tail4; idx += blockDim.x) {
+            const int head = idx / tail4, i = rot + ((idx - head * tail4) << 2);
+            __nv_bfloat16* dst = head < nq
+                ? qrow + head * hd
+                : kcache + ((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd;
+            store4(dst + i, value4(head * hd + i));
+        }
+        if (slot < 0) return;
+        const int q4 = hd >> 2;
+        for (int idx = threadIdx.x; idx < nkv * q4; idx += blockDim.x) {
+            const int head = idx / q4, i = (idx - head * q4) << 2;
+            store4(vcache + ((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i,
+                   value4((nq + nkv + head) * hd + i));
+        }
+        return;
+    }
+    for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
+        const int head = idx / half, i = idx - head * half;
+        const float a = value(head * hd + i), b = value(head * hd + i + half);
+        const float c = cs[i], s = cs[half + i];
+        const __nv_bfloat16 o1 = __float2bfloat16_rn(a * c - b * s);
+        const __nv_bfloat16 o2 = __float2bfloat16_rn(b * c + a * s);
+        if (head < nq) {
+            qrow[head * hd + i] = o1;
+            qrow[head * hd + i + half] = o2;
+        } else {
+            __nv_bfloat16* kc = kcache + ((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd;
+            kc[i] = o1;
+            kc[i + half] = o2;
+        }
+    }
+    const int tail = hd - rot;
+    for (int idx = threadIdx.x; idx < heads * tail; idx += blockDim.x) {
+        const int head = idx / tail, i = rot + (idx - head * tail);
+        const __nv_bfloat16 o = __float2bfloat16_rn(value(head * hd + i));
+        if (head < nq) qrow[head * hd + i] = o;
+        else kcache[((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd + i] = o;
+    }
+    if (slot < 0) return;
+    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+        const int head = idx / hd, i = idx - head * hd;
+        vcache[((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i] =
+            __float2bfloat16_rn(value((nq + nkv) * hd + idx));
+    }
+}
+
 // ------------------------------------------------------------- SiLU * up
-// out[t, i] = silu(gu[t, i]) * gu[t, I + i],  silu(z) = z / (1 + exp(-z))
+// out[t, i] = silu(gate) * up,  silu(z) = z / (1 + exp(-z)).
+// `interleaved`: gate and up alternate along the row (g0, u0, g1, u1, ...) instead of lying in
+// two halves; that is how a product over row-interleaved gate/up weights comes out.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n) {
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n,
+                                int interleaved) {
     if ((I & 3) == 0) {
         const size_t n4 = n >> 2;
         const int I4 = I >> 2;
         for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < n4;
              idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
             const size_t t = idx / I4, i = (idx - t * I4) << 2;
-            const F4 g = load4(gu + t * 2 * I + i), u = load4(gu + t * 2 * I + I + i);
+            F4 g, u;
+            if (interleaved) {
+                const F4 a = load4(gu + t * 2 * I + 2 * i), b = load4(gu + t * 2 * I + 2 * i + 4);
+                g = F4{{a.v[0], a.v[2], b.v[0], b.v[2]}};
+                u = F4{{a.v[1], a.v[3], b.v[1], b.v[3]}};
+            } else {
+                g = load4(gu + t * 2 * I + i);
+                u = load4(gu + t * 2 * I + I + i);
+            }
             F4 r;
 #pragma unroll
             for (int k = 0; k < 4; ++k) r.v[k] = g.v[k] / (1.0f + expf(-g.v[k])) * u.v[k];
@@ -222,8 +349,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
     for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < n;
          idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const size_t t = idx / I, i = idx - t * I;
-        const float g = to_float(gu[t * 2 * I + i]);
-        const float u = to_float(gu[t * 2 * I + I + i]);
+        const float g = to_float(gu[t * 2 * I + (interleaved ? 2 * i : i)]);
+        const float u = to_float(gu[t * 2 * I + (interleaved ? 2 * i + 1 : I + i)]);
         out[idx] = from_float<T>(g / (1.0f + expf(-g)) * u);
     }
 }
@@ -245,10 +372,11 @@ SOMI_API int somi_embed(const int* ids, const void* table, int dtype, float* out
 }
 
 SOMI_API int somi_add_rmsnorm(float* residual, const void* delta, int delta_dtype,
-                              const void* weight, int weight_dtype, float eps, void* out,
+                              int delta_splits, long long delta_split_stride, const void* weight, int weight_dtype, float eps, void* out,
                               int out_dtype, const int* rows, int n_out, int H, int write_back,
                               cudaStream_t stream) {
     if (n_out <= 0) return 0;
+    if (delta_splits < 1 || (delta_splits > 1 && delta_dtype != SOMI_F32)) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>(H) * sizeof(float);
     if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
@@ -258,7 +386,8 @@ SOMI_API int somi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
             cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,                                     \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
         add_rmsnorm_kernel<TD, TO><<<n_out, threads, smem, stream>>>(                            \
-            residual, static_cast<const TD*>(delta), weight, weight_dtype, eps,                  \
+            residual, static_cast<const TD*>(delta), delta_splits, delta_split_stride, weight,   \
+            weight_dtype, eps,                                                                   \
             static_cast<TO*>(out), rows, H, write_back);                                         \
     } while (0)
     if (delta_dtype == SOMI_F32 && out_dtype == SOMI_F32) SOMI_LAUNCH_NORM(float, float);
@@ -286,8 +415,23 @@ SOMI_API int somi_rope_store(void* qkv, int dtype, const int* positions, const f
     return launch_status();
 }
 
+SOMI_API int somi_rope_store_partial(const float* parts, int splits, long long split_stride,
+                                     const void* bias, int bias_dtype, void* q_out,
+                                     const int* positions, const float* inv_freq, int T, int nq,
+                                     int nkv, int hd, int rot, const int* slot_map, void* kcache,
+                                     void* vcache, int page_size, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rot < 0 || rot > hd || (rot & 1) || splits < 1) return SOMI_ERR_UNSUPPORTED;
+    const size_t smem = static_cast<size_t>(rot > 0 ? rot : 2) * sizeof(float);
+    rope_store_partial_kernel<<<T, 256, smem, stream>>>(
+        parts, splits, split_stride, bias, bias_dtype, static_cast<__nv_bfloat16*>(q_out),
+        positions, inv_freq, nq, nkv, hd, rot, slot_map, static_cast<__nv_bfloat16*>(kcache),
+        static_cast<__nv_bfloat16*>(vcache), page_size);
+    return launch_status();
+}
+
 SOMI_API int somi_silu_mul(const void* gu, void* out, int dtype, long long T, int I,
-                           cudaStream_t stream) {
+                           int interleaved, cudaStream_t stream) {
     const size_t n = static_cast<size_t>(T) * I;
     if (n == 0) return 0;
     const int threads = 256;
@@ -295,9 +439,9 @@ SOMI_API int somi_silu_mul(const void* gu, void* out, int dtype, long long T, in
     const int blocks = static_cast<int>(work / threads + 1 < 148 * 16 ? work / threads + 1 : 148 * 16);
     if (dtype == SOMI_F32)
         silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(
-            static_cast<const float*>(gu), static_cast<float*>(out), I, n);
+            static_cast<const float*>(gu), static_cast<float*>(out), I, n, interleaved);
     else
         silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
-            static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), I, n);
+            static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), I, n, interleaved);
     return launch_status();
 }

@@ -69,7 +69,7 @@ __device__ __forceinline__ void tcgen05_fence_after() {
 
 // TOK: tokens padded to the MMA's N (16, 32, 64).  STAGES: depth of the shared-memory ring.
 template <int TOK, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, (STAGES <= 4 ? 2 : 1))
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                    const __grid_constant__ CUtensorMap x_map, int M, int N, int K,
                    int kb_per_split, int mode, const void* __restrict__ bias, int bias_dtype,
@@ -261,7 +261,7 @@ SOMI_API int somi_gemm_error() {
 // x tensor map was made with (16, 32 or 64) and must be >= M.
 SOMI_API int somi_skinny_gemm(const void* w_map, const void* x_map, int x_box_rows, int M, int N,
                               int K, int splits, int mode, const void* bias, int bias_dtype,
-                              void* out, cudaStream_t stream) {
+                              void* out, int deep_ring, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > x_box_rows || K % 8 != 0 || K <= 0 || mode < 0 || mode > 3) return SOMI_ERR_UNSUPPORTED;
     if (mode == kGemmSwiGLU && (N & 1)) return SOMI_ERR_UNSUPPORTED;
@@ -269,10 +269,15 @@ SOMI_API int somi_skinny_gemm(const void* w_map, const void* x_map, int x_box_ro
     const CUtensorMap* wm = static_cast<const CUtensorMap*>(w_map);
     const CUtensorMap* xm = static_cast<const CUtensorMap*>(x_map);
     const long long stride = static_cast<long long>(M) * N;
+    // deep_ring: one CTA per SM with an 8-stage ring; otherwise two CTAs per SM with 4 stages
+    // each, so that one CTA's prologue and epilogue overlap the other's main loop.
+#define SOMI_SKINNY(TOK, ST) \
+    return launch_skinny<TOK, ST>(wm, xm, M, N, K, splits, mode, bias, bias_dtype, out, stride, stream)
     switch (x_box_rows) {
-        case 16: return launch_skinny<16, 8>(wm, xm, M, N, K, splits, mode, bias, bias_dtype, out, stride, stream);
-        case 32: return launch_skinny<32, 8>(wm, xm, M, N, K, splits, mode, bias, bias_dtype, out, stride, stream);
-        case 64: return launch_skinny<64, 8>(wm, xm, M, N, K, splits, mode, bias, bias_dtype, out, stride, stream);
+        case 16: if (deep_ring) SOMI_SKINNY(16, 8); else SOMI_SKINNY(16, 4);
+        case 32: if (deep_ring) SOMI_SKINNY(32, 8); else SOMI_SKINNY(32, 4);
+        case 64: if (deep_ring) SOMI_SKINNY(64, 8); else SOMI_SKINNY(64, 4);
         default: return SOMI_ERR_UNSUPPORTED;
     }
+#undef SOMI_SKINNY
 }

@@ -102,23 +102,49 @@ class CudaOps:
         self._done(rc, "embed")
 
     def add_rmsnorm(self, residual, delta, weight, eps, out, rows=None) -> None:
+        """residual += delta (float32, in place); out = rmsnorm(residual) * weight.
+
+        `delta` is [N, H] in the compute dtype, or float32 [splits, N, H] partial sums that are
+        added in order.  With `rows`, only those rows are produced and residual is not written.
+        """
         _check(residual, delta, weight, out, rows)
         assert residual.dtype == torch.float32
         H = residual.shape[1]
         n_out = out.shape[0]
+        splits, stride = 1, 0
+        if delta is not None and delta.dim() == 3:
+            assert delta.dtype == torch.float32
+            splits, stride = delta.shape[0], delta.shape[1] * delta.shape[2]
         rc = self.lib.somi_add_rmsnorm(
             _ptr(residual), _ptr(delta), _code(delta) if delta is not None else _F32,
+            ctypes.c_int(splits), ctypes.c_longlong(stride),
             _ptr(weight), _code(weight), ctypes.c_float(eps), _ptr(out), _code(out), _ptr(rows),
             ctypes.c_int(n_out), ctypes.c_int(H), ctypes.c_int(0 if rows is not None else 1),
             self._stream())
         self._done(rc, "add_rmsnorm")
 
     def rope_store(self, qkv, positions, inv_freq, nq, nkv, hd, rotary_dim, slot_map, kcache,
-                   vcache) -> None:
-        _check(qkv, positions, inv_freq, slot_map, kcache, vcache)
+                   vcache, partials=None, bias=None) -> None:
+        """Rotate q and k of `qkv` in place and store k, v at their cache slots.
+
+        With `partials` (float32 [splits, T, width], the output of a split-K projection) the
+        projection is summed here, `bias` added, and `qkv` (bfloat16) only receives the queries.
+        """
+        _check(qkv, positions, inv_freq, slot_map, kcache, vcache, partials, bias)
         page_size = kcache.shape[2] if kcache is not None else 1
         if kcache is not None and slot_map is not None:
             assert kcache.dtype == qkv.dtype and vcache.dtype == qkv.dtype
+        if partials is not None:
+            assert partials.dtype == torch.float32 and qkv.dtype == torch.bfloat16
+            rc = self.lib.somi_rope_store_partial(
+                _ptr(partials), ctypes.c_int(partials.shape[0]),
+                ctypes.c_longlong(partials.shape[1] * partials.shape[2]), _ptr(bias),
+                _code(bias) if bias is not None else _F32, _ptr(qkv), _ptr(positions),
+                _ptr(inv_freq), ctypes.c_int(qkv.shape[0]), ctypes.c_int(nq), ctypes.c_int(nkv),
+                ctypes.c_int(hd), ctypes.c_int(rotary_dim), _ptr(slot_map), _ptr(kcache),
+                _ptr(vcache), ctypes.c_int(page_size), self._stream())
+            self._done(rc, "rope_store_partial")
+            return
         rc = self.lib.somi_rope_store(
             _ptr(qkv), _code(qkv), _ptr(positions), _ptr(inv_freq), ctypes.c_int(qkv.shape[0]),
             ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(rotary_dim),
@@ -240,14 +266,22 @@ class CudaOps:
             if max_splits > 1:
                 self.launches += 1
 
-    def silu_mul(self, gu: torch.Tensor, out: torch.Tensor) -> None:
+    def silu_mul(self, gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
+        """out = silu(gate) * up; gate/up are the two halves of `gu`'s rows, or alternate."""
         _check(gu, out)
         rc = self.lib.somi_silu_mul(_ptr(gu), _ptr(out), _code(gu), ctypes.c_longlong(gu.shape[0]),
-                                    ctypes.c_int(out.shape[1]), self._stream())
+                                    ctypes.c_int(out.shape[1]), ctypes.c_int(1 if interleaved else 0),
+                                    self._stream())
         self._done(rc, "silu_mul")
 
     # ------------------------------------------------------- tcgen05 matrix product
     GEMM_BF16, GEMM_F32, GEMM_PARTIAL_F32, GEMM_SWIGLU = 0, 1, 2, 3
+
+    def skinny_splits(self, N: int, K: int) -> int:
+        """How many ranges of K to run side by side so that about two CTAs per SM are busy."""
+        tiles = -(-N // 128)
+        k_blocks = -(-K // 64)
+        return max(1, min(296 // tiles, k_blocks // 4, 16))
 
     def skinny_supported(self, M: int, N: int, K: int, dtype) -> bool:
         """Whether the tensor-memory kernel takes x[M, K] @ w[N, K]^T (few tokens, bfloat16)."""
@@ -273,7 +307,7 @@ class CudaOps:
         return entry[1]
 
     def skinny_gemm(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None,
-                    mode: int = 0, splits: int = 1) -> torch.Tensor:
+                    mode: int = 0, splits: int = 1, deep_ring: bool = False) -> torch.Tensor:
         """x[M, K] @ w[N, K]^T on tcgen05 tensor cores for M <= 64.
 
         mode GEMM_BF16 -> bf16 [M, N] (+ bias); GEMM_F32 -> float32 [M, N];
@@ -298,7 +332,8 @@ class CudaOps:
             ctypes.c_void_p(self._gemm_map(w, 128)), ctypes.c_void_p(self._gemm_map(x, box)),
             ctypes.c_int(box), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
             ctypes.c_int(splits), ctypes.c_int(mode), _ptr(bias),
-            _code(bias) if bias is not None else _F32, _ptr(out), self._stream())
+            _code(bias) if bias is not None else _F32, _ptr(out),
+            ctypes.c_int(1 if deep_ring else 0), self._stream())
         self._done(rc, "skinny_gemm")
         return out
 

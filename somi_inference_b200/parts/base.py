@@ -10,7 +10,9 @@ Interfaces (duck-typed; the classes below only document them):
 * Norm:          `forward(residual, delta=None, rows=None) -> Tensor`
                  adds `delta` into the fp32 `residual` (in place) and returns the
                  normalised rows in the compute dtype; with `rows`, only those
-                 rows are produced and `residual` is left untouched.
+                 rows are produced and `residual` is left untouched.  `delta` is
+                 what a mixer or feed-forward returned: [T, H], or float32
+                 [splits, T, H] partial sums that the norm adds up in order.
 * FeedForward:   `forward(x, batch) -> Tensor` of the same shape as `x`.
 * Mixer:         `cache_needs() -> CacheNeeds`, and
                  `forward(x, batch, cache, owns_cache) -> Tensor`.

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from .base import BuildContext, TensorDecl, names_of
-from .linear import project_to_float32
+from .linear import Linear
 from .registry import EMBEDDINGS, HEADS
 
 
@@ -46,7 +46,7 @@ class LMHead:
     def __init__(self, params, tensors, ctx: BuildContext) -> None:
         n = names_of(params)
         self.ctx = ctx
-        self.weight = tensors[n["tied_to"] if params["tied"] else n["weight"]]
+        self.proj = Linear(tensors[n["tied_to"] if params["tied"] else n["weight"]], None, ctx.ops)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return project_to_float32(h, self.weight)
+        return self.proj.to_float32(h)

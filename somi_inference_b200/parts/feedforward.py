@@ -31,12 +31,18 @@ class SwiGLU:
         n = names_of(params)
         self.ctx = ctx
         self.inter = int(params["intermediate_size"])
-        self.gate_up = Linear(torch.cat([tensors[n["gate_weight"]], tensors[n["up_weight"]]], 0)
-                              .contiguous())
-        self.down = Linear(tensors[n["down_weight"]])
+        # rows alternate gate_i, up_i, so that one thread pair of the product's epilogue (or one
+        # vector load of the activation kernel) holds a matching gate and up
+        gate, up = tensors[n["gate_weight"]], tensors[n["up_weight"]]
+        self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.inter, -1).contiguous(),
+                              None, ctx.ops)
+        self.down = Linear(tensors[n["down_weight"]], None, ctx.ops)
 
     def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
-        gu = self.gate_up(x)
-        act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
-        self.ctx.ops.silu_mul(gu, act)
-        return self.down(act)
+        act = self.gate_up.swiglu(x)
+        if act is None:
+            gu = self.gate_up(x)
+            act = torch.empty((x.shape[0], self.inter), dtype=x.dtype, device=x.device)
+            self.ctx.ops.silu_mul(gu, act, interleaved=True)
+        partial = self.down.partial_sums(act)
+        return partial if partial is not None else self.down(act)

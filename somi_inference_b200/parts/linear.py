@@ -1,9 +1,12 @@
-"""Dense projection y = x W^T (+ b) through the library matrix product.
+"""Dense projection y = x W^T (+ b).
 
 The reference's engine uses `nn.Linear` for every projection
-(somi_inference/models/qwen2.py:221-222,268-271), i.e. the library GEMM; so does
-this class.  In float32 the product is a true 32-bit one: the reduced-precision
-matrix mode (TF32) is switched off process-wide when the package is imported.
+(somi_inference/models/qwen2.py:221-222,268-271), i.e. the library GEMM.  Here a step with few
+tokens (bfloat16, at most `ops.skinny_max_tokens` rows) runs the engine's own tcgen05 kernel,
+which streams the weight once through TMA and tensor memory and can leave split-K partial sums
+or apply SiLU(gate)*up in its epilogue; everything else (prompt portions, float32) goes to the
+library product.  In float32 that product is a true 32-bit one: the reduced-precision matrix
+mode (TF32) is switched off process-wide when the package is imported.
 """
 
 from __future__ import annotations
@@ -13,19 +16,45 @@ import torch.nn.functional as F
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None) -> None:
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None, ops=None) -> None:
         self.weight = weight                      # [out, in], compute dtype
         self.bias = None if bias is None else bias.to(weight.dtype)
+        self.ops = ops
+        self.out_features, self.in_features = weight.shape
+
+    def skinny(self, x: torch.Tensor) -> bool:
+        ops = self.ops
+        return (ops is not None and x.is_cuda and getattr(ops, "skinny_supported", None) is not None
+                and ops.skinny_supported(x.shape[0], self.out_features, self.in_features, x.dtype))
 
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if self.skinny(x):
+            return self.ops.skinny_gemm(x, self.weight, self.bias, self.ops.GEMM_BF16)
         return F.linear(x, self.weight, self.bias)
 
+    def partial_sums(self, x: torch.Tensor) -> torch.Tensor | None:
+        """float32 [splits, M, out] partial sums over ranges of K (bias in the first), for a
+        consumer that adds them up (the next norm, the rotary kernel); None when the step is not
+        one for the tcgen05 kernel."""
+        if not self.skinny(x):
+            return None
+        ops = self.ops
+        return ops.skinny_gemm(x, self.weight, self.bias, ops.GEMM_PARTIAL_F32,
+                               splits=ops.skinny_splits(self.out_features, self.in_features))
 
-def project_to_float32(h: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """h W^T with a float32 result (the library product accumulates in float32)."""
-    if h.dtype == torch.float32:
-        return F.linear(h, weight)
-    try:
-        return torch.mm(h, weight.t(), out_dtype=torch.float32)
-    except (TypeError, RuntimeError):
-        return F.linear(h, weight).float()
+    def swiglu(self, x: torch.Tensor) -> torch.Tensor | None:
+        """silu(gate) * up for a weight whose rows alternate gate, up; None when not available."""
+        if not self.skinny(x):
+            return None
+        return self.ops.skinny_gemm(x, self.weight, None, self.ops.GEMM_SWIGLU)
+
+    def to_float32(self, x: torch.Tensor) -> torch.Tensor:
+        """x W^T with a float32 result (accumulation is float32 in every path)."""
+        if x.dtype == torch.float32:
+            return F.linear(x, self.weight)
+        if self.skinny(x):
+            return self.ops.skinny_gemm(x, self.weight, None, self.ops.GEMM_F32)
+        try:
+            return torch.mm(x, self.weight.t(), out_dtype=torch.float32)
+        except (TypeError, RuntimeError):
+            return F.linear(x, self.weight).float()

@@ -60,9 +60,9 @@ class AttentionMixer:
         if params.get("qkv_bias"):
             b = torch.cat([tensors[n["q_bias"]].float(), tensors[n["k_bias"]].float(),
                            tensors[n["v_bias"]].float()], 0)
-        self.qkv = Linear(w.contiguous(), b)
+        self.qkv = Linear(w.contiguous(), b, ctx.ops)
         self.out = Linear(tensors[n["o_weight"]],
-                          tensors[n["o_bias"]] if params.get("out_bias") else None)
+                          tensors[n["o_bias"]] if params.get("out_bias") else None, ctx.ops)
         self.position = POSITION_ENCODINGS.build(params["position"], tensors, ctx)
         ctx.ops.check_attention_geometry(self.num_heads, self.num_kv_heads, self.head_dim)
 
@@ -70,14 +70,23 @@ class AttentionMixer:
         return CacheNeeds(paged=PagedKVNeeds(self.num_kv_heads, self.head_dim, self.window))
 
     def forward(self, x: torch.Tensor, batch, cache, owns_cache: bool) -> torch.Tensor:
-        qkv = self.qkv(x)
         paged = cache.paged
-        self.position.encode_and_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim,
-                                       batch, paged, owns_cache)
+        partial = self.qkv.partial_sums(x) if self.position.takes_partial_sums else None
+        if partial is not None:
+            # the split-K product's partial sums (the bias is in the first) are added up by the
+            # rotary kernel itself
+            qkv = torch.empty((x.shape[0], self.qkv.out_features), dtype=x.dtype, device=x.device)
+            self.position.encode_and_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim,
+                                           batch, paged, owns_cache, partials=partial)
+        else:
+            qkv = self.qkv(x)
+            self.position.encode_and_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim,
+                                           batch, paged, owns_cache)
         out = torch.empty((x.shape[0], self.num_heads * self.head_dim), dtype=x.dtype,
                           device=x.device)
         self.ctx.ops.paged_attention(qkv, paged.keys, paged.values, batch,
                                      batch.groups[paged.group], self.num_heads,
                                      self.num_kv_heads, self.head_dim, self.scale,
                                      self.window, out, storage=paged.storage)
-        return self.out(out)
+        partial = self.out.partial_sums(out)
+        return partial if partial is not None else self.out(out)

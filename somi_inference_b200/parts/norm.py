@@ -29,6 +29,7 @@ class RMSNorm:
 
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None = None,
                 rows: torch.Tensor | None = None) -> torch.Tensor:
+        """`delta` is [T, size], or float32 [splits, T, size] partial sums that are added up."""
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.size), dtype=self.ctx.dtype, device=residual.device)
         self.ctx.ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows)

@@ -12,7 +12,9 @@ to their cache slots.
 
 A position encoding answers
     encode_and_store(qkv, num_heads, num_kv_heads, head_dim, batch, paged, write)
-where `qkv` is [T, (num_heads + 2 num_kv_heads) * head_dim], rotated in place.
+where `qkv` is [T, (num_heads + 2 num_kv_heads) * head_dim], rotated in place.  One that sets
+`takes_partial_sums = True` also accepts `partials=` (float32 [splits, T, width] partial sums of
+the projection) and `bias=`, adds them up itself and leaves the queries in `qkv`.
 """
 
 from __future__ import annotations
@@ -40,14 +42,17 @@ class RotaryEncoding:
         exponent = torch.arange(0, self.rotary_dim, 2) / self.rotary_dim
         self.inv_freq = (1.0 / (self.theta ** exponent)).to(torch.float32).to(ctx.device)
 
-    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, batch, paged, write):
+    takes_partial_sums = True     # encode_and_store accepts `partials=` and `bias=`
+
+    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, batch, paged, write,
+                         partials=None, bias=None):
         group = batch.groups[paged.group] if paged is not None else None
         self.ctx.ops.rope_store(
             qkv, batch.positions, self.inv_freq, num_heads, num_kv_heads, head_dim,
             self.rotary_dim,
             group.slot_map if (write and group is not None) else None,
             paged.keys if paged is not None else None,
-            paged.values if paged is not None else None)
+            paged.values if paged is not None else None, partials=partials, bias=bias)
 
 
 @POSITION_ENCODINGS.register("none")
@@ -58,14 +63,17 @@ class NoPositionEncoding:
     def declare(params) -> list[TensorDecl]:
         return []
 
+    takes_partial_sums = True
+
     def __init__(self, params, tensors, ctx: BuildContext) -> None:
         self.ctx = ctx
         self.inv_freq = torch.zeros(1, dtype=torch.float32, device=ctx.device)
 
-    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, batch, paged, write):
+    def encode_and_store(self, qkv, num_heads, num_kv_heads, head_dim, batch, paged, write,
+                         partials=None, bias=None):
         group = batch.groups[paged.group] if paged is not None else None
         self.ctx.ops.rope_store(
             qkv, batch.positions, self.inv_freq, num_heads, num_kv_heads, head_dim, 0,
             group.slot_map if (write and group is not None) else None,
             paged.keys if paged is not None else None,
-            paged.values if paged is not None else None)
+            paged.values if paged is not None else None, partials=partials, bias=bias)

@@ -25,7 +25,12 @@ class HostOps:
     def embed(self, ids, table, out) -> None:
         out.copy_(table[ids.long()].float())
 
+    def skinny_supported(self, M, N, K, dtype) -> bool:
+        return False
+
     def add_rmsnorm(self, residual, delta, weight, eps, out, rows=None) -> None:
+        if delta is not None and delta.dim() == 3:
+            delta = delta.sum(0)
         if rows is None:
             if delta is not None:
                 residual += delta.float()
@@ -38,8 +43,11 @@ class HostOps:
         out.copy_((r * inv * weight.float()).to(out.dtype))
 
     def rope_store(self, qkv, positions, inv_freq, nq, nkv, hd, rotary_dim, slot_map, kcache,
-                   vcache) -> None:
+                   vcache, partials=None, bias=None) -> None:
         T = qkv.shape[0]
+        if partials is not None:
+            full = partials.sum(0) + (bias.float() if bias is not None else 0.0)
+            qkv.copy_(full.to(qkv.dtype))
         x = qkv.view(T, nq + 2 * nkv, hd)
         if rotary_dim:
             ang = positions.float().unsqueeze(1) * inv_freq.unsqueeze(0)     # [T, rot/2]
@@ -84,9 +92,12 @@ class HostOps:
             o = torch.einsum("htn,nhd->thd", torch.softmax(s, -1), v)
             out[a:b] = o.reshape(b - a, nq * hd).to(out.dtype)
 
-    def silu_mul(self, gu, out) -> None:
+    def silu_mul(self, gu, out, interleaved=False) -> None:
         I = out.shape[1]
-        g, u = gu[:, :I].float(), gu[:, I:].float()
+        if interleaved:
+            g, u = gu[:, 0::2].float(), gu[:, 1::2].float()
+        else:
+            g, u = gu[:, :I].float(), gu[:, I:].float()
         out.copy_((g / (1.0 + torch.exp(-g)) * u).to(out.dtype))
 
     def sample(self, logits, temperature, top_k, top_p, penalty, seed, counter, hist_off,

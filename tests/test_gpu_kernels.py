@@ -241,3 +241,68 @@ def test_tensor_core_prefill_attention(ops, case):
     HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), cb, cb.groups[0], nq, nkv,
                          hd, hd ** -0.5, window, ref)
     torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(torch.bfloat16))
+
+
+def test_add_rmsnorm_sums_partial_deltas(ops):
+    g = torch.Generator().manual_seed(5)
+    N, H, S = 7, 896, 5
+    res = torch.randn(N, H, generator=g)
+    parts = torch.randn(S, N, H, generator=g)
+    w = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    r_gpu = res.clone().cuda()
+    out = torch.empty(N, H, dtype=torch.bfloat16, device="cuda")
+    ops.add_rmsnorm(r_gpu, parts.cuda(), w.cuda(), 1e-6, out)
+    r_ref = res.clone()
+    ref = torch.empty(N, H, dtype=torch.bfloat16)
+    HOST.add_rmsnorm(r_ref, parts, w, 1e-6, ref)
+    torch.testing.assert_close(r_gpu.cpu(), r_ref, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(torch.bfloat16))
+    rows = torch.tensor([6, 2], dtype=torch.int32)
+    out2 = torch.empty(2, H, dtype=torch.bfloat16, device="cuda")
+    ops.add_rmsnorm(res.clone().cuda(), parts.cuda(), w.cuda(), 1e-6, out2, rows.cuda())
+    torch.testing.assert_close(out2.cpu().float(), ref[rows.long()].float(), **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("nq,nkv,hd,rot,ps", [(14, 2, 64, 64, 16), (28, 4, 128, 128, 16), (6, 3, 80, 32, 32)])
+@pytest.mark.parametrize("store", [True, False])
+def test_rope_store_from_partial_sums(ops, nq, nkv, hd, rot, ps, store):
+    g = torch.Generator().manual_seed(6)
+    T, pages, S = 9, 4, 3
+    width = (nq + 2 * nkv) * hd
+    parts = torch.randn(S, T, width, generator=g)
+    bias = torch.randn(width, generator=g).to(torch.bfloat16)
+    positions = torch.randint(0, 5000, (T,), generator=g, dtype=torch.int32)
+    inv_freq = (1.0 / (1e4 ** (torch.arange(0, rot, 2) / rot))).float()
+    slots = torch.randperm(pages * ps, generator=g)[:T].to(torch.int32)
+    kc = torch.zeros(pages, nkv, ps, hd, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q_gpu = torch.zeros(T, width, dtype=torch.bfloat16, device="cuda")
+    kc_gpu, vc_gpu = kc.clone().cuda(), vc.clone().cuda()
+    ops.rope_store(q_gpu, positions.cuda(), inv_freq.cuda(), nq, nkv, hd, rot,
+                   slots.cuda() if store else None, kc_gpu, vc_gpu, partials=parts.cuda(),
+                   bias=bias.cuda())
+    # reference: the summed projection in float32, rotated, then rounded once
+    full = (parts.sum(0) + bias.float())
+    q_ref = full.clone()
+    kc_ref, vc_ref = kc.float(), vc.float()
+    HOST.rope_store(q_ref, positions, inv_freq, nq, nkv, hd, rot, slots if store else None,
+                    kc_ref, vc_ref)
+    t = dict(rtol=1.6e-2, atol=2e-2)
+    torch.testing.assert_close(q_gpu.cpu().float()[:, :nq * hd], q_ref[:, :nq * hd], **t)
+    if store:
+        torch.testing.assert_close(kc_gpu.cpu().float(), kc_ref, **t)
+        torch.testing.assert_close(vc_gpu.cpu().float(), vc_ref, **t)
+    else:
+        assert kc_gpu.abs().sum().item() == 0 and vc_gpu.abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(3, 176), (5, 4864), (2, 90)])
+def test_silu_mul_interleaved(ops, dtype, T, I):
+    g = torch.Generator().manual_seed(8)
+    gu = (torch.randn(T, 2 * I, generator=g) * 3).to(dtype)
+    out = torch.empty(T, I, dtype=dtype, device="cuda")
+    ops.silu_mul(gu.cuda(), out, interleaved=True)
+    ref = torch.empty(T, I, dtype=dtype)
+    HOST.silu_mul(gu, ref, interleaved=True)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(dtype))

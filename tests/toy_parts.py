@@ -89,6 +89,8 @@ class ToyRoutedFF:
 class ToyShiftEncoding:
     """q[..., 0] and k[..., 0] get position * step added; keys and values are then stored."""
 
+    takes_partial_sums = False
+
     @staticmethod
     def declare(params):
         return []
