@@ -50,6 +50,8 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     unsigned char* Ks = Qs + kDecRows * HD * 2;                 // [128][HD] bf16
     unsigned char* Vs = Ks + kDecChunk * HD * 2;                // [128][HD] bf16
     __shared__ float m_s[4][kDecRows], l_s[4][kDecRows];
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int split = blockIdx.x, kvh = blockIdx.y, i = blockIdx.z;
     const int req = req_base + i, row = row_base + i;
@@ -222,6 +224,8 @@ paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restr
                           int max_splits, const int* __restrict__ ctx_len, int row_base,
                           int req_base, int nq, int window, __nv_bfloat16* __restrict__ out) {
     const int i = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const DecodeRange rg = decode_range(ctx_len[req_base + i], window);
     if (rg.n_splits - rg.first_split == 1) return;       // written by the split kernel
     const size_t base = (static_cast<size_t>(i) * nq + head) * max_splits;
@@ -246,7 +250,7 @@ int launch_decode(const void* qkv, int row_stride, int row_base, int req_base, i
         cudaFuncSetAttribute(paged_decode_split_kernel<HD>,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(max_splits, nkv, n_decode);
-    paged_decode_split_kernel<HD><<<grid, kDecThreads, smem, stream>>>(
+    launch_pdl(paged_decode_split_kernel<HD>, dim3(grid), dim3(kDecThreads), smem, stream, 
         static_cast<const __nv_bfloat16*>(qkv), row_stride, row_base, req_base,
         static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache),
         block_table, bt_stride, ctx_len, nq, nkv, page_size, scale * 1.4426950408889634f, window,
@@ -254,7 +258,7 @@ int launch_decode(const void* qkv, int row_stride, int row_base, int req_base, i
     int rc = launch_status();
     if (rc != 0 || max_splits == 1) return rc;
     dim3 mgrid(n_decode, nq);
-    paged_decode_merge_kernel<HD><<<mgrid, HD, 0, stream>>>(
+    launch_pdl(paged_decode_merge_kernel<HD>, dim3(mgrid), dim3(HD), 0, stream, 
         part_o, part_ml, max_splits, ctx_len, row_base, req_base, nq, window,
         static_cast<__nv_bfloat16*>(out));
     return launch_status();

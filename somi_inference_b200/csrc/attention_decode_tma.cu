@@ -64,6 +64,8 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     unsigned char* Ps = Qs + kTdRows * HD * 2;    // [16][128 keys] bf16, software swizzle
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ float m_s[kTdWarps][kTdRows], l_s[kTdWarps][kTdRows];
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int split = blockIdx.x, kvh = blockIdx.y, i = blockIdx.z;
     const int req = req_base + i, row = row_base + i;
@@ -259,6 +261,8 @@ paged_decode_tma_merge_kernel(const float* __restrict__ part_o, const float* __r
                               int max_splits, const int* __restrict__ ctx_len, int row_base,
                               int req_base, int nq, int window, __nv_bfloat16* __restrict__ out) {
     const int i = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     const TdRange rg = td_range(ctx_len[req_base + i], window);
     if (rg.n_splits - rg.first_split == 1) return;
     const size_t base = (static_cast<size_t>(i) * nq + head) * max_splits;
@@ -284,7 +288,7 @@ int launch_tma_decode(const CUtensorMap* map, const void* qkv, int row_stride, i
     cudaFuncSetAttribute(paged_decode_tma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
     dim3 grid(max_splits, nkv, n_decode);
-    paged_decode_tma_kernel<HD><<<grid, kTdThreads, smem, stream>>>(
+    launch_pdl(paged_decode_tma_kernel<HD>, dim3(grid), dim3(kTdThreads), smem, stream, 
         *map, static_cast<const __nv_bfloat16*>(qkv), row_stride, row_base, req_base, k_row0,
         v_row0, block_table, bt_stride, ctx_len, nq, nkv, page_size,
         scale * 1.4426950408889634f, window, part_o, part_ml, max_splits,
@@ -292,7 +296,7 @@ int launch_tma_decode(const CUtensorMap* map, const void* qkv, int row_stride, i
     int rc = launch_status();
     if (rc != 0 || max_splits == 1) return rc;
     dim3 mgrid(n_decode, nq);
-    paged_decode_tma_merge_kernel<HD><<<mgrid, HD, 0, stream>>>(
+    launch_pdl(paged_decode_tma_merge_kernel<HD>, dim3(mgrid), dim3(HD), 0, stream, 
         part_o, part_ml, max_splits, ctx_len, row_base, req_base, nq, window,
         static_cast<__nv_bfloat16*>(out));
     return launch_status();

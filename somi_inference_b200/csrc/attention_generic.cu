@@ -30,6 +30,8 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, int row_stride,
                                int n_prefill_tok, int nq, int nkv, int hd, int page_size,
                                float scale, int window, T* __restrict__ out) {
     extern __shared__ float smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     float* Qs = smem;                           // [kBM][hd]
     float* Ks = Qs + kBM * hd;                  // [kBN][hd + 1]
     float* Vs = Ks + kBN * (hd + 1);            // [kBN][hd]
@@ -164,7 +166,7 @@ SOMI_API int somi_paged_attention_generic(
         if (smem > 48 * 1024)                                                                   \
             cudaFuncSetAttribute(paged_attention_generic_kernel<T>,                             \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        paged_attention_generic_kernel<T><<<grid, kThreads, smem, stream>>>(                    \
+        launch_pdl(paged_attention_generic_kernel<T>, dim3(grid), dim3(kThreads), smem, stream,                     \
             static_cast<const T*>(qkv), row_stride, static_cast<const T*>(kcache),              \
             static_cast<const T*>(vcache), block_table, bt_stride, cu_q, ctx_len, tiles,        \
             n_tiles, n_prefill_req, n_prefill_tok, nq, nkv, hd, page_size, scale, window,       \

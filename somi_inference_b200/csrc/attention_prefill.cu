@@ -58,6 +58,8 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     unsigned char* Qs = smem_raw;                               // [64][HD]
     unsigned char* Ks = Qs + kPfBM * HD * 2;                    // 2 x [64][HD]
     unsigned char* Vs = Ks + 2 * TILE;                          // 2 x [64][HD]
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int req = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1];
     const int rows = tiles[3 * blockIdx.x + 2];
@@ -206,7 +208,7 @@ int launch_prefill(const void* qkv, int row_stride, const void* kcache, const vo
         cudaFuncSetAttribute(paged_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)smem);
     dim3 grid(n_tiles, nq);
-    paged_prefill_kernel<HD><<<grid, kPfThreads, smem, stream>>>(
+    launch_pdl(paged_prefill_kernel<HD>, dim3(grid), dim3(kPfThreads), smem, stream, 
         static_cast<const __nv_bfloat16*>(qkv), row_stride,
         static_cast<const __nv_bfloat16*>(kcache), static_cast<const __nv_bfloat16*>(vcache),
         block_table, bt_stride, cu_q, ctx_len, tiles, nq, nkv, page_size,

@@ -66,4 +66,37 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 
+// ---- programmatic dependent launch
+// Every kernel of this library is launched with the programmatic-serialization attribute: it
+// may be scheduled while its predecessor in the stream is still running, so that its launch
+// latency and its set-up (barriers, tensor memory, index arithmetic) overlap the predecessor's
+// tail.  The rule that makes this safe: a kernel calls `pdl_wait()` before its first access to
+// global memory that another kernel writes or reads, and before any early return; it calls
+// `pdl_launch_dependents()` as its first statement so that its own successor may be scheduled.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+
+inline int& pdl_enabled() {
+    static int on = 1;
+    return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                      cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+}
+
 }  // namespace somi

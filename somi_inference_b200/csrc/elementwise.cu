@@ -53,6 +53,8 @@ __device__ __forceinline__ F4 load4_any(const void* p, int dtype, size_t i) {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                              float* __restrict__ out, int H) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const T* row = table + static_cast<size_t>(ids[t]) * H;
     float* o = out + static_cast<size_t>(t) * H;
@@ -77,6 +79,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    int write_back) {
     extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const int b = blockIdx.x;
     const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
     float* r = residual + row * H;
@@ -135,6 +139,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   int rot, const int* __restrict__ slot_map,
                                   T* __restrict__ kcache, T* __restrict__ vcache, int page_size) {
     extern __shared__ float cs[];   // cos[rot/2], sin[rot/2]
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const float pos = static_cast<float>(positions[t]);
@@ -220,6 +226,8 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
                                           __nv_bfloat16* __restrict__ kcache,
                                           __nv_bfloat16* __restrict__ vcache, int page_size) {
     extern __shared__ float cs[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int width = (nq + 2 * nkv) * hd;
@@ -324,6 +332,8 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t n,
                                 int interleaved) {
+    pdl_launch_dependents();
+    pdl_wait();
     if ((I & 3) == 0) {
         const size_t n4 = n >> 2;
         const int I4 = I >> 2;
@@ -359,14 +369,17 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, i
 
 using namespace somi;
 
+// Switches programmatic dependent launch on (default) or off for every kernel of the library.
+SOMI_API void somi_set_pdl(int on) { pdl_enabled() = on ? 1 : 0; }
+
 SOMI_API int somi_embed(const int* ids, const void* table, int dtype, float* out, int T, int H,
                         cudaStream_t stream) {
     if (T <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
     if (dtype == SOMI_F32)
-        embed_kernel<float><<<T, threads, 0, stream>>>(ids, static_cast<const float*>(table), out, H);
+        launch_pdl(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, ids, static_cast<const float*>(table), out, H);
     else
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
+        launch_pdl(embed_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, 
             ids, static_cast<const __nv_bfloat16*>(table), out, H);
     return launch_status();
 }
@@ -385,7 +398,7 @@ SOMI_API int somi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
         if (smem > 48 * 1024)                                                                    \
             cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,                                     \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        add_rmsnorm_kernel<TD, TO><<<n_out, threads, smem, stream>>>(                            \
+        launch_pdl(add_rmsnorm_kernel<TD, TO>, dim3(n_out), dim3(threads), smem, stream,                             \
             residual, static_cast<const TD*>(delta), delta_splits, delta_split_stride, weight,   \
             weight_dtype, eps,                                                                   \
             static_cast<TO*>(out), rows, H, write_back);                                         \
@@ -405,11 +418,11 @@ SOMI_API int somi_rope_store(void* qkv, int dtype, const int* positions, const f
     if (rot < 0 || rot > hd || (rot & 1)) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>(rot > 0 ? rot : 2) * sizeof(float);
     if (dtype == SOMI_F32)
-        rope_store_kernel<float><<<T, 256, smem, stream>>>(
+        launch_pdl(rope_store_kernel<float>, dim3(T), dim3(256), smem, stream, 
             static_cast<float*>(qkv), positions, inv_freq, nq, nkv, hd, rot, slot_map,
             static_cast<float*>(kcache), static_cast<float*>(vcache), page_size);
     else
-        rope_store_kernel<__nv_bfloat16><<<T, 256, smem, stream>>>(
+        launch_pdl(rope_store_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, stream, 
             static_cast<__nv_bfloat16*>(qkv), positions, inv_freq, nq, nkv, hd, rot, slot_map,
             static_cast<__nv_bfloat16*>(kcache), static_cast<__nv_bfloat16*>(vcache), page_size);
     return launch_status();
@@ -423,7 +436,7 @@ SOMI_API int somi_rope_store_partial(const float* parts, int splits, long long s
     if (T <= 0) return 0;
     if (rot < 0 || rot > hd || (rot & 1) || splits < 1) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>(rot > 0 ? rot : 2) * sizeof(float);
-    rope_store_partial_kernel<<<T, 256, smem, stream>>>(
+    launch_pdl(rope_store_partial_kernel, dim3(T), dim3(256), smem, stream, 
         parts, splits, split_stride, bias, bias_dtype, static_cast<__nv_bfloat16*>(q_out),
         positions, inv_freq, nq, nkv, hd, rot, slot_map, static_cast<__nv_bfloat16*>(kcache),
         static_cast<__nv_bfloat16*>(vcache), page_size);
@@ -438,10 +451,10 @@ SOMI_API int somi_silu_mul(const void* gu, void* out, int dtype, long long T, in
     const size_t work = (I & 3) == 0 ? n / 4 : n;
     const int blocks = static_cast<int>(work / threads + 1 < 148 * 16 ? work / threads + 1 : 148 * 16);
     if (dtype == SOMI_F32)
-        silu_mul_kernel<float><<<blocks, threads, 0, stream>>>(
+        launch_pdl(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, 
             static_cast<const float*>(gu), static_cast<float*>(out), I, n, interleaved);
     else
-        silu_mul_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(
+        launch_pdl(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, 
             static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), I, n, interleaved);
     return launch_status();
 }

@@ -84,6 +84,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
 
+    pdl_launch_dependents();      // the next kernel may be scheduled; it waits for this one itself
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n0 = blockIdx.x * kGemmBN;
     const int split = blockIdx.y;
@@ -111,10 +112,25 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_d = tmem_base_s;
+    // Barriers and tensor memory are set up.  The weights do not depend on the preceding kernel,
+    // so the producer fills the ring's first stages with W tiles before it waits for that kernel;
+    // the activation tiles, and everything any other thread reads or writes, come after the wait.
+    const int n_pre = min(nkb, STAGES);
+    if (warp == 0 && lane == 0) {
+        for (int kb = 0; kb < n_pre; ++kb) {
+            const uint32_t fb = smem_u32(&full_bar[kb]);
+            mbar_expect_tx(fb, StageBytes);
+            tma_load_2d(smem_u32(stages + kb * StageBytes), &w_map, (kb0 + kb) * kGemmBK, n0, fb);
+        }
+    }
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < nkb; ++kb) {
+            for (int kb = 0; kb < n_pre; ++kb)
+                tma_load_2d(smem_u32(stages + kb * StageBytes + kGemmWBytes), &x_map,
+                            (kb0 + kb) * kGemmBK, 0, smem_u32(&full_bar[kb]));
+            for (int kb = n_pre; kb < nkb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
                 if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1)) { failed_s = 1; break; }
@@ -220,7 +236,7 @@ int launch_skinny(const CUtensorMap* w_map, const CUtensorMap* x_map, int M, int
     const int nkb = (K + kGemmBK - 1) / kGemmBK;
     const int kbps = (nkb + splits - 1) / splits;
     dim3 grid((N + kGemmBN - 1) / kGemmBN, (nkb + kbps - 1) / kbps);
-    skinny_gemm_kernel<TOK, STAGES><<<grid, kGemmThreads, smem, stream>>>(
+    launch_pdl(skinny_gemm_kernel<TOK, STAGES>, dim3(grid), dim3(kGemmThreads), smem, stream, 
         *w_map, *x_map, M, N, K, kbps, mode, bias, bias_dtype, out, out_split_stride);
     return launch_status();
 }

@@ -56,6 +56,8 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
     __shared__ float sh_total;
     __shared__ int sh_found;
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     const float temp = temperature[row];
@@ -79,9 +81,24 @@ sample_kernel(const float* __restrict__ logits, int V, const float* __restrict__
     // ---- maximum and its lowest index
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = tid; i < V; i += kSampleThreads) {
-        const float v = x.at(i);
-        if (v > best) { best = v; best_i = i; }
+    if (!use_pen && (V & 3) == 0) {
+        // four logits per load, several loads in flight: this pass is all a greedy row needs
+        const float4* row4 = reinterpret_cast<const float4*>(x.logits);
+        const float it = x.inv_temperature;
+#pragma unroll 4
+        for (int i = tid; i < (V >> 2); i += kSampleThreads) {
+            const float4 q = row4[i];
+            const float v0 = q.x * it, v1 = q.y * it, v2 = q.z * it, v3 = q.w * it;
+            if (v0 > best) { best = v0; best_i = 4 * i; }
+            if (v1 > best) { best = v1; best_i = 4 * i + 1; }
+            if (v2 > best) { best = v2; best_i = 4 * i + 2; }
+            if (v3 > best) { best = v3; best_i = 4 * i + 3; }
+        }
+    } else {
+        for (int i = tid; i < V; i += kSampleThreads) {
+            const float v = x.at(i);
+            if (v > best) { best = v; best_i = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -259,7 +276,7 @@ SOMI_API int somi_sample(const float* logits, int rows, int V, const float* temp
     if (smem > 160 * 1024) return SOMI_ERR_UNSUPPORTED;      // vocabularies beyond 1.3 M tokens
     if (smem > 40 * 1024)
         cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    sample_kernel<<<rows, kSampleThreads, smem, stream>>>(logits, V, temperature, top_k, top_p,
+    launch_pdl(sample_kernel, dim3(rows), dim3(kSampleThreads), smem, stream, logits, V, temperature, top_k, top_p,
                                                          penalty, seed, counter, hist_off,
                                                          hist_tok, out);
     return launch_status();

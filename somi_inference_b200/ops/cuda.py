@@ -183,6 +183,10 @@ class CudaOps:
             self._tensor_maps[key] = entry
         return entry[1]
 
+    def set_pdl(self, on: bool) -> None:
+        """Programmatic dependent launch for all kernels of the library (on by default)."""
+        self.lib.somi_set_pdl(ctypes.c_int(1 if on else 0))
+
     def check_errors(self) -> None:
         """Raise if a kernel recorded that one of its bounded waits ran out (synchronises)."""
         if int(self.lib.somi_decode_tma_error()) != 0:
