@@ -9,6 +9,7 @@ compiled library, construction fails.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -71,6 +72,8 @@ class CudaOps:
         self.skinny_max_tokens = int(self.lib.somi_skinny_gemm_max_tokens())
         self._retired: list = []
         self.launches = 0     # kernels of this library launched so far
+        if os.environ.get("SOMI_B200_PDL", "1") == "0":
+            self.set_pdl(False)
 
     # ------------------------------------------------------------------ util
     @staticmethod
@@ -281,16 +284,22 @@ class CudaOps:
     # ------------------------------------------------------- tcgen05 matrix product
     GEMM_BF16, GEMM_F32, GEMM_PARTIAL_F32, GEMM_SWIGLU = 0, 1, 2, 3
 
-    def skinny_splits(self, N: int, K: int) -> int:
-        """How many ranges of K to run side by side so that about two CTAs per SM are busy."""
+    def skinny_splits(self, M: int, N: int, K: int) -> int:
+        """How many ranges of K to run side by side: enough CTAs for about two per SM, at least
+        four K blocks each, and partial sums (4 * splits * M * N bytes, written and read back)
+        that stay below a quarter of the weight's own bytes."""
         tiles = -(-N // 128)
         k_blocks = -(-K // 64)
-        return max(1, min(296 // tiles, k_blocks // 4, 16))
+        return max(1, min(296 // tiles, k_blocks // 4, K // (16 * M), 16))
 
     def skinny_supported(self, M: int, N: int, K: int, dtype) -> bool:
         """Whether the tensor-memory kernel takes x[M, K] @ w[N, K]^T (few tokens, bfloat16)."""
-        return (self.use_skinny_gemm and dtype == torch.bfloat16 and 1 <= M <= self.skinny_max_tokens
-                and K % 8 == 0 and N >= 1)
+        if not (self.use_skinny_gemm and dtype == torch.bfloat16
+                and 1 <= M <= self.skinny_max_tokens and K % 8 == 0 and N >= 1):
+            return False
+        # measured: above 16 tokens a matrix below 8 Mi elements is latency-bound on the few
+        # CTAs this kernel gives it, and the library's product is faster
+        return M <= 16 or N * K >= (8 << 20)
 
     def _gemm_map(self, t: torch.Tensor, box_rows: int) -> int:
         key = (t.data_ptr(), t.shape[0], t.shape[1], box_rows)
@@ -332,6 +341,10 @@ class CudaOps:
             out = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
         else:
             out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        # few CTAs: one per SM with the whole shared memory as an 8-stage ring (a CTA's stream
+        # is bound by the bytes it keeps in flight); many CTAs: two per SM with 4 stages each
+        ctas = -(-N // 128) * (splits if mode == self.GEMM_PARTIAL_F32 else 1)
+        deep_ring = deep_ring or ctas <= 148
         rc = self.lib.somi_skinny_gemm(
             ctypes.c_void_p(self._gemm_map(w, 128)), ctypes.c_void_p(self._gemm_map(x, box)),
             ctypes.c_int(box), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),

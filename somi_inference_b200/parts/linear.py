@@ -40,7 +40,7 @@ class Linear:
             return None
         ops = self.ops
         return ops.skinny_gemm(x, self.weight, self.bias, ops.GEMM_PARTIAL_F32,
-                               splits=ops.skinny_splits(self.out_features, self.in_features))
+                               splits=ops.skinny_splits(x.shape[0], self.out_features, self.in_features))
 
     def swiglu(self, x: torch.Tensor) -> torch.Tensor | None:
         """silu(gate) * up for a weight whose rows alternate gate, up; None when not available."""
