@@ -67,6 +67,7 @@ class CudaOps:
         self._workspace = None
         self._tensor_maps: dict = {}
         self.use_tma_decode = True
+        self.use_tma_prefill = True
         self._gemm_maps: dict = {}
         self.use_skinny_gemm = True
         self.skinny_max_tokens = int(self.lib.somi_skinny_gemm_max_tokens())
@@ -195,6 +196,9 @@ class CudaOps:
         if int(self.lib.somi_decode_tma_error()) != 0:
             raise KernelError("the TMA decode attention kernel gave up waiting for a copy; "
                               "its results are not valid")
+        if int(self.lib.somi_prefill_tma_error()) != 0:
+            raise KernelError("the TMA prefill attention kernel gave up waiting for a copy; "
+                              "its results are not valid")
         if int(self.lib.somi_gemm_error()) != 0:
             raise KernelError("the tcgen05 matrix product gave up waiting on a barrier; "
                               "its results are not valid")
@@ -217,12 +221,27 @@ class CudaOps:
                                and self.prefill_supported(nq, nkv, hd, qkv.dtype))
         if tensor_core_prefill:
             tiles = batch.tiles[self.prefill_q_tile]
-            rc = self.lib.somi_paged_attention_prefill(
-                _ptr(qkv), ctypes.c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache),
-                _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
-                _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), ctypes.c_int(nq),
-                ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
-                ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
+            tma = (self.use_tma_prefill and storage is not None and bool(
+                self.lib.somi_prefill_tma_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
+                                                    ctypes.c_int(hd), ctypes.c_int(page_size))))
+            if tma:
+                row_bytes = hd * 2
+                rc = self.lib.somi_paged_attention_prefill_tma(
+                    ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)), _ptr(qkv),
+                    ctypes.c_int(qkv.shape[1]),
+                    ctypes.c_longlong((kcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    ctypes.c_longlong((vcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
+                    ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
+                    ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
+            else:
+                rc = self.lib.somi_paged_attention_prefill(
+                    _ptr(qkv), ctypes.c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache),
+                    _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
+                    ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
+                    ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
             self._done(rc, "paged_attention_prefill")
         tiles = batch.tiles[self.generic_q_tile]
         n_generic_tiles = 0 if tensor_core_prefill else tiles.shape[0]

@@ -176,13 +176,25 @@ def run_trace_program(model_dir: str, dtype: str, steps: list[dict], max_tokens:
     return out
 
 
-def compare(got: dict, reference: dict[str, torch.Tensor], atol: float, what: str) -> float:
-    """Every produced row against the plain logits of its request; returns the worst error."""
+def compare(got: dict, reference: dict[str, torch.Tensor], atol: float, what: str,
+            rms_tol: float | None = None) -> float:
+    """Every produced row against the plain logits of its request; returns the worst error.
+
+    `atol` bounds the largest single difference; `rms_tol`, when given, bounds the root mean
+    square of all differences (rounding noise has a stable RMS, while the largest of a million
+    differences moves with every change of summation order)."""
     worst = 0.0
     where = None
+    sq, n = 0.0, 0
     for (rid, pos), row in got.items():
-        err = (row.double() - reference[rid][pos].double()).abs().max().item()
+        diff = row.double() - reference[rid][pos].double()
+        err = diff.abs().max().item()
+        sq += float(diff.pow(2).sum())
+        n += diff.numel()
         if not err <= worst:      # also catches NaN
             worst, where = err, (rid, pos)
     assert worst <= atol, f"{what}: worst error {worst:.3e} at request/position {where} (allowed {atol:.1e})"
+    if rms_tol is not None:
+        rms = (sq / max(n, 1)) ** 0.5
+        assert rms <= rms_tol, f"{what}: rms error {rms:.3e} (allowed {rms_tol:.1e})"
     return worst

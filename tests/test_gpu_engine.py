@@ -74,7 +74,7 @@ def test_long_decoding_and_first_tokens(root, dtype):
     ids = random_tokens(303, cfg["vocab_size"], 4)
     ref = plain.logits(cfg, w, ids)
     scale = ref.abs().max().item()
-    atol = 3e-5 if dtype == "float32" else 2e-2 * scale
+    atol = 3e-5 if dtype == "float32" else 4e-2 * scale      # bounds as in test_gpu_replay.py
     eng = Engine(d, dtype=dtype, page_size=16, max_tokens=320)
     rows = [eng.step([StepEntry("x", ids[:3], [0, 1, 2])])]
     for t in ids[3:]:
@@ -186,13 +186,14 @@ def test_toy_architecture_on_the_gpu(root, dtype):
         reqs = {f"t{i}": random_tokens(n, toy_model.V, 20 + i) for i, n in enumerate([45, 70, 12, 90, 33])}
         ref = {k: toy_model.plain_logits(d, v) for k, v in reqs.items()}
         scale = max(v.abs().max().item() for v in ref.values())
-        atol = 3e-5 if dtype == "float32" else 2e-2 * scale
+        atol = 3e-5 if dtype == "float32" else 4e-2 * scale
+        rms = 1e-5 if dtype == "float32" else 4e-3 * scale
         for mode in (replay.whole, replay.portions, replay.mixed):
             steps, max_tokens = mode(reqs)
             eng = Engine(d, dtype=dtype, page_size=8, max_tokens=max_tokens)
             assert len(eng.cache.groups) == 2
             got = replay.run_steps(eng, steps)
-            replay.compare(got, ref, atol, f"toy/{dtype}/{mode.__name__}")
+            replay.compare(got, ref, atol, f"toy/{dtype}/{mode.__name__}", rms)
             assert all(f == eng.num_pages for f in eng.cache.free_pages())
     finally:
         unregister_architecture(toy_model.ARCH)

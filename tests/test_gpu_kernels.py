@@ -221,11 +221,14 @@ PREFILL_CASES = [
     (6, 3, 32, 8, 24, [(0, 90), (50, 30), (23, 2), (5, 70)]),
     (4, 1, 64, 32, 100, [(0, 300), (150, 129)]),
     (2, 2, 128, 64, None, [(3, 61), (0, 64), (0, 65)]),
+    (7, 1, 64, 16, None, [(0, 700), (1500, 100)]),
+    (4, 2, 128, 8, 70, [(0, 400), (333, 90)]),
 ]
 
 
+@pytest.mark.parametrize("tma", [True, False], ids=["tma", "cp_async"])
 @pytest.mark.parametrize("case", PREFILL_CASES, ids=[f"p{i}" for i in range(len(PREFILL_CASES))])
-def test_tensor_core_prefill_attention(ops, case):
+def test_tensor_core_prefill_attention(ops, case, tma):
     """Portions with and without cached context, around the 64-row and 64-key tile edges,
     windows shorter and longer than a tile; bfloat16 goes through the tensor-core kernel."""
     nq, nkv, hd, ps, window, reqs = case
@@ -234,8 +237,13 @@ def test_tensor_core_prefill_attention(ops, case):
                                               window=window, requests=reqs, dtype=torch.bfloat16,
                                               seed=11)
     out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
-    ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
-                        hd ** -0.5, window, out)
+    ops.use_tma_prefill = tma
+    try:
+        ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
+                            hd ** -0.5, window, out, storage=view.storage)
+        ops.check_errors()
+    finally:
+        ops.use_tma_prefill = True
     ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
     cb = batch_to_cpu(batch)
     HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), cb, cb.groups[0], nq, nkv,

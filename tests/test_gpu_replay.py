@@ -23,11 +23,15 @@ STD = 0.08
 LENGTHS = [5, 97, 40, 70, 33, 100, 64, 81]
 # float32: logits are of size 3-5; differences between orders of summation stay below 3e-5.
 # bfloat16: every activation that passes between kernels is rounded to 8 bits of mantissa
-# (2^-9 relative each); the bound is stated relative to the largest logit of the model, 2e-2
-# of it (about ten such roundings compounded).  It was measured first on whole prompts, where
-# no cache or batching is involved (worst 1.7e-2 of the largest logit), and is the same for
-# every way of cutting: a fault of the cache or the batch moves logits by the logits' own size.
-ATOL = {"float32": lambda scale: 3e-5, "bfloat16": lambda scale: 2e-2 * scale}
+# (2^-9 relative each).  Measured on whole prompts (no cache or batching involved) and under
+# every cut and every kernel variant (TMA or cp.async attention, tcgen05 or library products):
+# the root mean square of the logit differences is 1.0e-3 to 2.4e-3 of the largest logit and
+# hardly moves, while the largest single difference among a million logits moves between
+# 0.5e-2 and 2.0e-2 with the order of summation.  Bounds: RMS 4e-3 and largest 4e-2 of the
+# largest logit, the same for every way of cutting; a fault of the cache or the batch moves a
+# position's logits by the logits' own size, twenty-five times the bound.
+ATOL = {"float32": lambda scale: 3e-5, "bfloat16": lambda scale: 4e-2 * scale}
+RMS = {"float32": lambda scale: 1e-5, "bfloat16": lambda scale: 4e-3 * scale}
 MODES = {"whole": replay.whole, "last32": replay.last_one_by_one, "portions": replay.portions,
          "mixed": replay.mixed}
 
@@ -58,7 +62,7 @@ def test_replay_in_process(models, name, dtype, mode):
     eng = Engine(d, dtype=dtype, page_size=PAGE_SIZES[name], max_tokens=max_tokens)
     got = replay.run_steps(eng, steps)
     assert len(got) >= sum(1 for _ in reqs)
-    replay.compare(got, ref, ATOL[dtype](scale), f"{name}/{dtype}/{mode}")
+    replay.compare(got, ref, ATOL[dtype](scale), f"{name}/{dtype}/{mode}", RMS[dtype](scale))
     assert all(f == eng.num_pages for f in eng.cache.free_pages()), "pages were lost"
 
 
@@ -71,7 +75,7 @@ def test_replay_program(models, tmp_path, name, dtype):
         steps, max_tokens = MODES[mode](sub)
         out_dir = str(tmp_path / mode)
         got = replay.run_trace_program(d, dtype, steps, max_tokens, out_dir, cfg["vocab_size"])
-        replay.compare(got, ref, ATOL[dtype](scale), f"trace_run {name}/{dtype}/{mode}")
+        replay.compare(got, ref, ATOL[dtype](scale), f"trace_run {name}/{dtype}/{mode}", RMS[dtype](scale))
 
 
 def test_cut_independence_float32(models):
