@@ -71,6 +71,9 @@ class StepBatch:
     layout_key: tuple = field(default_factory=tuple)   # sizes that fix every offset in the buffer
 
 
+_NO_TILES = np.zeros((0, 3), dtype=np.int64)
+
+
 def _align(n: int, a: int = 4) -> int:
     return -(-n // a) * a
 
@@ -89,12 +92,14 @@ class BatchBuilder:
         self.width_step = max(1, 512 // cache.page_size)     # table columns come in steps of 512 tokens
         self._capacity = 0
         self._turn = 0
+        self._decode_views: dict = {}
         self._alloc(capacity_ints)
 
     def _alloc(self, capacity: int) -> None:
         pin = self.device.type == "cuda"
         self._host = [torch.empty(capacity, dtype=torch.int32, pin_memory=pin) for _ in range(2)]
         self._events = [None, None]
+        self._event_pool = [torch.cuda.Event(), torch.cuda.Event()] if pin else [None, None]
         self._dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
         self._capacity = capacity
 
@@ -112,6 +117,8 @@ class BatchBuilder:
         """
         if not entries:
             raise ValueError("a step needs at least one entry")
+        if all(len(e.tokens) == 1 for e in entries):
+            return self._build_decode(entries)
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) <= 1, i))
         R = len(entries)
         q_lens = np.array([len(entries[i].tokens) for i in order], dtype=np.int64)
@@ -190,32 +197,11 @@ class BatchBuilder:
         sizes = [T, T, T, R + 1, R, R, K] + [3 * len(tiles_np[bm]) for bm in self.q_tile_sizes]
         for gi in range(len(tables)):
             sizes += [R * widths[gi], T]
-        offsets = []
-        off = 0
-        for s in sizes:
-            offsets.append(off)
-            off += _align(max(s, 1))
-        total = off
-        if total > self._capacity:
-            torch.cuda.synchronize() if self.device.type == "cuda" else None
-            self._alloc(max(total, 2 * self._capacity))
-        self._turn ^= 1
-        ev = self._events[self._turn]
-        if ev is not None:
-            ev.synchronize()
-        host = self._host[self._turn].numpy()
         arrays = [token_ids, positions, token_req, cu_q, ctx, slots, np.array(rows, dtype=np.int64)]
         arrays += [tiles_np[bm].reshape(-1) for bm in self.q_tile_sizes]
         for gi in range(len(tables)):
             arrays += [tables[gi].reshape(-1), slot_maps[gi]]
-        for a, o, s in zip(arrays, offsets, sizes):
-            host[o:o + s] = a
-        self._dev[:total].copy_(self._host[self._turn][:total], non_blocking=True)
-        if self.device.type == "cuda":
-            ev = torch.cuda.Event()
-            ev.record()
-            self._events[self._turn] = ev
-        self._last_bytes = total * 4
+        offsets, total = self._upload(sizes, arrays)
 
         def dv(k: int) -> torch.Tensor:
             return self._dev[offsets[k]:offsets[k] + sizes[k]]
@@ -236,3 +222,108 @@ class BatchBuilder:
             layout_key=tuple(sizes),
         )
         return batch, order
+
+    # ------------------------------------------------------------ decode-only steps
+    def _build_decode(self, entries: Sequence[StepEntry]) -> tuple[StepBatch, list[int]]:
+        """The same layout for a step of single-token requests only, with plain lists where the
+        general path uses array operations: such steps are short, so the host's share counts."""
+        cache = self.cache
+        R = len(entries)
+        reqs = [e.request for e in entries]
+        if len(set(reqs)) != R:
+            raise ValueError("a request appears twice in one step")
+        toks = [int(e.tokens[0]) for e in entries]
+        if self.vocab_size is not None and not (0 <= min(toks) and max(toks) < self.vocab_size):
+            bad = next(t for t in toks if not 0 <= t < self.vocab_size)
+            raise ValueError(f"token id {bad} is outside the vocabulary of {self.vocab_size}")
+        ctx = [cache.length(r) for r in reqs]
+        slots = [cache.slot(r) for r in reqs]
+        max_kv = max(ctx) + 1
+        if self.max_positions is not None and max_kv > self.max_positions:
+            raise ValueError(f"a request would reach {max_kv} positions; the model has "
+                             f"{self.max_positions}")
+        rows: list[int] = []
+        for j, e in enumerate(entries):
+            for w in e.want:
+                if w != 0:
+                    raise ValueError(f"request {e.request!r}: wanted index {w} is outside its 1 token")
+                rows.append(j)
+        K = len(rows)
+        ps = cache.page_size
+        slots_np = np.asarray(slots, dtype=np.int64)
+        pos_np = np.asarray(ctx, dtype=np.int64)
+        widths, tables, slot_maps = [], [], []
+        ar = np.arange(R)
+        for gi in range(len(cache.groups)):
+            width = max(-(-max_kv // ps), 1)
+            width = min(-(-width // self.width_step) * self.width_step, cache.max_blocks)
+            table = cache.block_tables(gi, slots_np, width)
+            page = table[ar, pos_np // ps].astype(np.int64)
+            if (page < 0).any():
+                raise RuntimeError("a token of this step has no page (reserve was not called, "
+                                   "or the page fell out of its window)")
+            widths.append(width)
+            tables.append(table)
+            slot_maps.append(page * ps + pos_np % ps)
+        sizes = [R, R, R, R + 1, R, R, K] + [0] * len(self.q_tile_sizes)
+        for gi in range(len(tables)):
+            sizes += [R * widths[gi], R]
+        arrays = [toks, ctx, range(R), range(R + 1), ctx, slots, rows]
+        arrays += [() for _ in self.q_tile_sizes]
+        for gi in range(len(tables)):
+            arrays += [tables[gi].reshape(-1), slot_maps[gi]]
+        offsets, total = self._upload(sizes, arrays)
+        key = tuple(sizes)
+        views = self._decode_views.get(key)
+        if views is None or views[0] is not self._dev:
+            # the device views depend on the sizes only: made once per layout
+            def dv(k: int) -> torch.Tensor:
+                return self._dev[offsets[k]:offsets[k] + sizes[k]]
+
+            n_fixed = 7
+            tiles = {bm: dv(n_fixed + t).view(-1, 3) for t, bm in enumerate(self.q_tile_sizes)}
+            g0 = n_fixed + len(self.q_tile_sizes)
+            groups = [GroupBatch(dv(g0 + 2 * gi).view(R, widths[gi]), dv(g0 + 2 * gi + 1), widths[gi])
+                      for gi in range(len(tables))]
+            views = (self._dev, [dv(k) for k in range(7)], tiles, groups)
+            if len(self._decode_views) > 256:
+                self._decode_views.clear()
+            self._decode_views[key] = views
+        _, fixed, tiles, groups = views
+        batch = StepBatch(
+            num_tokens=R, num_requests=R, num_prefill_requests=0, num_prefill_tokens=0,
+            max_q_len=1, max_kv_len=max_kv, token_ids=fixed[0], positions=fixed[1],
+            token_request=fixed[2], cu_q=fixed[3], ctx_len=fixed[4], state_slot=fixed[5],
+            logit_rows=fixed[6], tiles=tiles, groups=groups,
+            host=HostBatch(cu_q=np.arange(R + 1, dtype=np.int64), ctx_len=pos_np,
+                           state_slot=slots_np, requests=reqs),
+            layout_key=tuple(sizes))
+        return batch, list(range(R))
+
+    def _upload(self, sizes, arrays) -> tuple[list[int], int]:
+        """Lay the arrays out (each section aligned to 16 bytes), fill the next pinned buffer
+        and copy it to the device in one transfer."""
+        offsets = []
+        off = 0
+        for n in sizes:
+            offsets.append(off)
+            off += _align(max(n, 1))
+        total = off
+        if total > self._capacity:
+            torch.cuda.synchronize() if self.device.type == "cuda" else None
+            self._alloc(max(total, 2 * self._capacity))
+        self._turn ^= 1
+        ev = self._events[self._turn]
+        if ev is not None:
+            ev.synchronize()
+        host = self._host[self._turn].numpy()
+        for a, o, n in zip(arrays, offsets, sizes):
+            if n:
+                host[o:o + n] = a
+        self._dev[:total].copy_(self._host[self._turn][:total], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = self._event_pool[self._turn]
+            ev.record()
+            self._events[self._turn] = ev
+        self._last_bytes = total * 4
+        return offsets, total

@@ -129,13 +129,14 @@ class Engine:
             self.cache.commit(e.request)
         return logits
 
-    def run_reserved(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def run_reserved(self, entries: Sequence[StepEntry], keep: bool = True) -> torch.Tensor:
         """As `step`, for a caller (the scheduler) that registered the requests and reserved
-        their pages itself and will commit afterwards."""
+        their pages itself and will commit afterwards.  With `keep=False` the returned logits
+        may be a buffer that the next step overwrites (the caller samples from it at once)."""
         batch, _ = self.builder.build(entries)
-        return self._run(batch)
+        return self._run(batch, keep)
 
-    def _run(self, batch: StepBatch) -> torch.Tensor:
+    def _run(self, batch: StepBatch, keep: bool = True) -> torch.Tensor:
         """Forward pass of one batch.  Steps that hold only single-token requests are launch
         bound, so their kernel sequence is captured in a CUDA graph the second time a layout
         (batch size, table width, wanted rows) is seen and replayed from then on; the batch
@@ -152,7 +153,8 @@ class Engine:
             graph, logits, launches = entry
             graph.replay()
             self.ops.launches += launches
-            return logits.clone()       # the graph's own output buffer is overwritten by the next replay
+            # the graph's own output buffer is overwritten by the next replay
+            return logits.clone() if keep else logits
         with torch.no_grad():
             logits = self.model.forward(batch, self.cache)      # also warms up the libraries
         self._seen[key] = self._seen.get(key, 0) + 1

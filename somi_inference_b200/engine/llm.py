@@ -98,12 +98,12 @@ class LLM:
         entries = []
         samplers = []
         for item in batch.items:
-            toks = item.request.all_tokens[item.start:item.start + item.num_tokens]
+            toks = item.request.tokens(item.start, item.num_tokens)
             entries.append(StepEntry(item.request.request_id, toks,
                                      [item.num_tokens - 1] if item.samples else []))
             if item.samples:
                 samplers.append(item.request)
-        logits = self.engine.run_reserved(entries)
+        logits = self.engine.run_reserved(entries, keep=False)     # sampled from at once
         sampled: dict[int, int] = {}
         if samplers:
             ids = self.sampler.sample(

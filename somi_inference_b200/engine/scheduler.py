@@ -67,6 +67,15 @@ class Request:
     def num_tokens(self) -> int:
         return len(self.prompt_tokens) + len(self.output_tokens)
 
+    def tokens(self, start: int, n: int) -> list[int]:
+        """Tokens [start, start + n) of prompt + output, without joining the two lists."""
+        p = len(self.prompt_tokens)
+        if start >= p:
+            return self.output_tokens[start - p:start - p + n]
+        if start + n <= p:
+            return self.prompt_tokens[start:start + n]
+        return self.prompt_tokens[start:] + self.output_tokens[:start + n - p]
+
 
 @dataclass
 class ScheduledItem:

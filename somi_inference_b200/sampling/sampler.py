@@ -21,6 +21,7 @@ class Sampler:
         self.ops = ops
         self.device = torch.device(device)
         self.h2d_bytes_last = 0
+        self._greedy: dict = {}
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                counters: Sequence[int], seeds: Sequence[int],
@@ -36,6 +37,18 @@ class Sampler:
             raise ValueError(f"logits must be 2D, got shape {tuple(logits.shape)}")
         if not (len(params) == len(counters) == len(seeds) == rows):
             raise ValueError("one SamplingParams, counter and seed per logits row is needed")
+        if all(p.temperature == 0.0 and p.repetition_penalty == 1.0 for p in params):
+            # argmax rows need neither seeds, counters nor histories: one cached parameter block
+            cached = self._greedy.get(rows)
+            if cached is None:
+                cached = self._pack(params, [0] * rows, [0] * rows, None)
+                self._greedy[rows] = cached
+            self.h2d_bytes_last = 0
+            return self._launch(logits, rows, *cached)
+        return self._launch(logits, rows, *self._pack(params, counters, seeds, histories))
+
+    def _pack(self, params, counters, seeds, histories):
+        rows = len(params)
         # one packed upload: 4 float/int arrays of `rows`, seeds as two int32 each, offsets, tokens
         hist_off = np.zeros(rows + 1, dtype=np.int64)
         toks: list[np.ndarray] = []
@@ -64,6 +77,9 @@ class Sampler:
             buf[h:h + n_hist] = np.concatenate(toks)
         self.h2d_bytes_last = buf.nbytes
         dev = torch.from_numpy(buf).to(self.device, non_blocking=True)
+        return dev, r8, o, h, n_hist
+
+    def _launch(self, logits, rows, dev, r8, o, h, n_hist):
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
         self.ops.sample(logits, dev[0:rows].view(torch.float32), dev[r8:r8 + rows],
                         dev[2 * r8:2 * r8 + rows].view(torch.float32),
