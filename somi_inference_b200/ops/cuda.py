@@ -75,6 +75,8 @@ class CudaOps:
         self.launches = 0     # kernels of this library launched so far
         if os.environ.get("SOMI_B200_PDL", "1") == "0":
             self.set_pdl(False)
+        if os.environ.get("SOMI_B200_SKINNY", "1") == "0":      # for A/B measurements
+            self.use_skinny_gemm = False
 
     # ------------------------------------------------------------------ util
     @staticmethod
@@ -316,9 +318,10 @@ class CudaOps:
         if not (self.use_skinny_gemm and dtype == torch.bfloat16
                 and 1 <= M <= self.skinny_max_tokens and K % 8 == 0 and N >= 1):
             return False
-        # measured: above 16 tokens a matrix below 8 Mi elements is latency-bound on the few
-        # CTAs this kernel gives it, and the library's product is faster
-        return M <= 16 or N * K >= (8 << 20)
+        # measured (CUDA graphs of back-to-back products, and whole decode steps at batch 32 and
+        # 64): above 16 tokens this kernel wins only where a CTA streams a long K range of a
+        # large matrix; short K (few stages per CTA) and small matrices go to the library
+        return M <= 16 or (K >= 2048 and N * K >= (32 << 20))
 
     def _gemm_map(self, t: torch.Tensor, box_rows: int) -> int:
         key = (t.data_ptr(), t.shape[0], t.shape[1], box_rows)
