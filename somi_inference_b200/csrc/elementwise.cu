@@ -1,6 +1,8 @@
 // Memory-bound kernels of a decoder step: embedding gather, residual sum fused
 // with RMS normalisation, rotary encoding fused with the cache write, SiLU(gate)*up.
 // All arithmetic is float32; inputs and outputs are float32 or bfloat16.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace somi {
@@ -128,6 +130,63 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
         o[i] = from_float<TO>(row_buf[i] * inv * load_as_float(weight, weight_dtype, i));
 }
 
+// The same for few rows: a cluster of CTAs shares one row, each CTA owning a slice of the
+// columns, and the slices' sums of squares meet through distributed shared memory.  With one CTA
+// per row a step of 8 tokens would keep 8 SMs busy; this keeps 8 * cluster size.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_cluster_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                           int splits, long long split_stride,
+                                           const void* __restrict__ weight, int weight_dtype,
+                                           float eps, TO* __restrict__ out,
+                                           const int* __restrict__ rows, int H, int write_back,
+                                           int cols_per_cta) {
+    namespace cg = cooperative_groups;
+    extern __shared__ __align__(16) float row_buf[];          // this CTA's slice of the row
+    __shared__ float scratch[33];
+    __shared__ float slice_ss;
+    cg::cluster_group cluster = cg::this_cluster();
+    pdl_launch_dependents();
+    pdl_wait();
+    const int csize = static_cast<int>(cluster.num_blocks());
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int b = blockIdx.x / csize;
+    const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
+    const int c0 = rank * cols_per_cta, c1 = min(H, c0 + cols_per_cta);
+    float* r = residual + row * H;
+    const TD* d = delta ? delta + row * H : nullptr;
+    float ss = 0.f;
+    for (int i = c0 + threadIdx.x * 4; i < c1; i += blockDim.x * 4) {
+        F4 v = load4(r + i);
+        if (d) {
+#pragma unroll 4
+            for (int sp = 0; sp < splits; ++sp) {
+                const F4 dv = load4(d + sp * split_stride + i);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v.v[k] += dv.v[k];
+            }
+            if (write_back) store4(r + i, v);
+        }
+        store4(row_buf + (i - c0), v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) ss += v.v[k] * v.v[k];
+    }
+    ss = block_sum(ss, scratch);
+    if (threadIdx.x == 0) slice_ss = ss;
+    cluster.sync();
+    float total = 0.f;
+    for (int k = 0; k < csize; ++k) total += *cluster.map_shared_rank(&slice_ss, k);
+    cluster.sync();            // nobody leaves while its neighbours still read its sum
+    const float inv = 1.0f / sqrtf(total / static_cast<float>(H) + eps);
+    TO* o = out + static_cast<size_t>(b) * H;
+    for (int i = c0 + threadIdx.x * 4; i < c1; i += blockDim.x * 4) {
+        F4 v = load4(row_buf + (i - c0));
+        const F4 w = load4_any(weight, weight_dtype, i);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v.v[k] = v.v[k] * inv * w.v[k];
+        store4(o + i, v);
+    }
+}
+
 // ------------------------------------------- rotary encoding + cache write
 // qkv: [T, (nq + 2 nkv) * hd].  For every token: rotate the first `rot` dims of
 // each query and key head by angle = position * inv_freq[i] (pairs i, i + rot/2),
@@ -224,7 +283,8 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
                                           const float* __restrict__ inv_freq, int nq, int nkv,
                                           int hd, int rot, const int* __restrict__ slot_map,
                                           __nv_bfloat16* __restrict__ kcache,
-                                          __nv_bfloat16* __restrict__ vcache, int page_size) {
+                                          __nv_bfloat16* __restrict__ vcache, int page_size,
+                                          int heads_per_cta) {
     extern __shared__ float cs[];
     pdl_launch_dependents();
     pdl_wait();
@@ -259,11 +319,14 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
     const int slot = slot_map ? slot_map[t] : -1;
     const int page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? slot % page_size : 0;
-    const int heads = slot >= 0 ? nq + nkv : nq;         // keys matter only if they are stored
+    // this CTA's share of the nq + 2 nkv heads (queries, keys, values in that order)
+    const int h0 = blockIdx.y * heads_per_cta, h1 = min(nq + 2 * nkv, h0 + heads_per_cta);
+    const int rot_end = min(h1, slot >= 0 ? nq + nkv : nq);    // keys matter only if they are stored
+    const int n_rot = max(0, rot_end - h0);
     if ((half & 3) == 0 && (hd & 3) == 0) {
         const int hq = half >> 2;
-        for (int idx = threadIdx.x; idx < heads * hq; idx += blockDim.x) {
-            const int head = idx / hq, i = (idx - head * hq) << 2;
+        for (int idx = threadIdx.x; idx < n_rot * hq; idx += blockDim.x) {
+            const int head = h0 + idx / hq, i = (idx % hq) << 2;
             const F4 a = value4(head * hd + i), b = value4(head * hd + i + half);
             F4 o1, o2;
 #pragma unroll
@@ -279,24 +342,24 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
             store4(dst + i + half, o2);
         }
         const int tail4 = (hd - rot) >> 2;
-        for (int idx = threadIdx.x; idx < heads * tail4; idx += blockDim.x) {
-            const int head = idx / tail4, i = rot + ((idx - head * tail4) << 2);
+        for (int idx = threadIdx.x; idx < n_rot * tail4; idx += blockDim.x) {
+            const int head = h0 + idx / tail4, i = rot + ((idx % tail4) << 2);
             __nv_bfloat16* dst = head < nq
                 ? qrow + head * hd
                 : kcache + ((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd;
             store4(dst + i, value4(head * hd + i));
         }
         if (slot < 0) return;
-        const int q4 = hd >> 2;
-        for (int idx = threadIdx.x; idx < nkv * q4; idx += blockDim.x) {
-            const int head = idx / q4, i = (idx - head * q4) << 2;
+        const int v0 = max(h0, nq + nkv), q4 = hd >> 2;
+        for (int idx = threadIdx.x; idx < max(0, h1 - v0) * q4; idx += blockDim.x) {
+            const int head = v0 + idx / q4 - (nq + nkv), i = (idx % q4) << 2;
             store4(vcache + ((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i,
                    value4((nq + nkv + head) * hd + i));
         }
         return;
     }
-    for (int idx = threadIdx.x; idx < heads * half; idx += blockDim.x) {
-        const int head = idx / half, i = idx - head * half;
+    for (int idx = threadIdx.x; idx < n_rot * half; idx += blockDim.x) {
+        const int head = h0 + idx / half, i = idx % half;
         const float a = value(head * hd + i), b = value(head * hd + i + half);
         const float c = cs[i], s = cs[half + i];
         const __nv_bfloat16 o1 = __float2bfloat16_rn(a * c - b * s);
@@ -311,17 +374,18 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
         }
     }
     const int tail = hd - rot;
-    for (int idx = threadIdx.x; idx < heads * tail; idx += blockDim.x) {
-        const int head = idx / tail, i = rot + (idx - head * tail);
+    for (int idx = threadIdx.x; idx < n_rot * tail; idx += blockDim.x) {
+        const int head = h0 + idx / tail, i = rot + idx % tail;
         const __nv_bfloat16 o = __float2bfloat16_rn(value(head * hd + i));
         if (head < nq) qrow[head * hd + i] = o;
         else kcache[((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd + i] = o;
     }
     if (slot < 0) return;
-    for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-        const int head = idx / hd, i = idx - head * hd;
+    const int v0 = max(h0, nq + nkv);
+    for (int idx = threadIdx.x; idx < max(0, h1 - v0) * hd; idx += blockDim.x) {
+        const int head = v0 + idx / hd - (nq + nkv), i = idx % hd;
         vcache[((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i] =
-            __float2bfloat16_rn(value((nq + nkv) * hd + idx));
+            __float2bfloat16_rn(value((nq + nkv + head) * hd + i));
     }
 }
 
@@ -392,13 +456,35 @@ SOMI_API int somi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     if (delta_splits < 1 || (delta_splits > 1 && delta_dtype != SOMI_F32)) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>(H) * sizeof(float);
     if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
+    // few rows of a wide model: spread each row over a cluster of CTAs
+    int cluster = 0;
+    if (n_out <= 32 && (H & 3) == 0) {
+        if (H >= 2048 && H % 32 == 0) cluster = 8;
+        else if (H >= 512 && H % 16 == 0) cluster = 4;
+    }
+    if (cluster) {
+        const int cols = H / cluster;                        // a multiple of 4
+        const size_t csmem = static_cast<size_t>(cols) * sizeof(float);
+        const int cthreads = cols >= 1024 ? 256 : 128;
+#define SOMI_LAUNCH_CNORM(TD, TO)                                                                \
+    launch_pdl_cluster(add_rmsnorm_cluster_kernel<TD, TO>, dim3(n_out * cluster), dim3(cthreads), \
+                       csmem, stream, cluster, residual, static_cast<const TD*>(delta),          \
+                       delta_splits, delta_split_stride, weight, weight_dtype, eps,              \
+                       static_cast<TO*>(out), rows, H, write_back, cols)
+        if (delta_dtype == SOMI_F32 && out_dtype == SOMI_F32) SOMI_LAUNCH_CNORM(float, float);
+        else if (delta_dtype == SOMI_BF16 && out_dtype == SOMI_BF16) SOMI_LAUNCH_CNORM(__nv_bfloat16, __nv_bfloat16);
+        else if (delta_dtype == SOMI_F32 && out_dtype == SOMI_BF16) SOMI_LAUNCH_CNORM(float, __nv_bfloat16);
+        else SOMI_LAUNCH_CNORM(__nv_bfloat16, float);
+#undef SOMI_LAUNCH_CNORM
+        return launch_status();
+    }
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
 #define SOMI_LAUNCH_NORM(TD, TO)                                                                 \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
             cudaFuncSetAttribute(add_rmsnorm_kernel<TD, TO>,                                     \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);        \
-        launch_pdl(add_rmsnorm_kernel<TD, TO>, dim3(n_out), dim3(threads), smem, stream,                             \
+        launch_pdl(add_rmsnorm_kernel<TD, TO>, dim3(n_out), dim3(threads), smem, stream,         \
             residual, static_cast<const TD*>(delta), delta_splits, delta_split_stride, weight,   \
             weight_dtype, eps,                                                                   \
             static_cast<TO*>(out), rows, H, write_back);                                         \
@@ -436,10 +522,13 @@ SOMI_API int somi_rope_store_partial(const float* parts, int splits, long long s
     if (T <= 0) return 0;
     if (rot < 0 || rot > hd || (rot & 1) || splits < 1) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>(rot > 0 ? rot : 2) * sizeof(float);
-    launch_pdl(rope_store_partial_kernel, dim3(T), dim3(256), smem, stream, 
+    // a token's heads are spread over several CTAs: few tokens would otherwise use few SMs
+    const int heads_per_cta = T > 32 ? nq + 2 * nkv : 4;
+    const int chunks = (nq + 2 * nkv + heads_per_cta - 1) / heads_per_cta;
+    launch_pdl(rope_store_partial_kernel, dim3(T, chunks), dim3(128), smem, stream,
         parts, splits, split_stride, bias, bias_dtype, static_cast<__nv_bfloat16*>(q_out),
         positions, inv_freq, nq, nkv, hd, rot, slot_map, static_cast<__nv_bfloat16*>(kcache),
-        static_cast<__nv_bfloat16*>(vcache), page_size);
+        static_cast<__nv_bfloat16*>(vcache), page_size, heads_per_cta);
     return launch_status();
 }
 

@@ -69,7 +69,7 @@ __device__ __forceinline__ void tcgen05_fence_after() {
 
 // TOK: tokens padded to the MMA's N (16, 32, 64).  STAGES: depth of the shared-memory ring.
 template <int TOK, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, (STAGES <= 4 ? 2 : 1))
+__global__ void __launch_bounds__(kGemmThreads, (STAGES <= 6 ? 2 : 1))
 skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                    const __grid_constant__ CUtensorMap x_map, int M, int N, int K,
                    int kb_per_split, int mode, const void* __restrict__ bias, int bias_dtype,
@@ -285,13 +285,14 @@ SOMI_API int somi_skinny_gemm(const void* w_map, const void* x_map, int x_box_ro
     const CUtensorMap* wm = static_cast<const CUtensorMap*>(w_map);
     const CUtensorMap* xm = static_cast<const CUtensorMap*>(x_map);
     const long long stride = static_cast<long long>(M) * N;
-    // deep_ring: one CTA per SM with an 8-stage ring; otherwise two CTAs per SM with 4 stages
-    // each, so that one CTA's prologue and epilogue overlap the other's main loop.
+    // deep_ring: one CTA per SM with an 8-stage ring; otherwise two CTAs per SM with 4 to 6
+    // stages each (what fits twice into shared memory), so that one CTA's prologue and epilogue
+    // overlap the other's main loop.
 #define SOMI_SKINNY(TOK, ST) \
     return launch_skinny<TOK, ST>(wm, xm, M, N, K, splits, mode, bias, bias_dtype, out, stride, stream)
     switch (x_box_rows) {
-        case 16: if (deep_ring) SOMI_SKINNY(16, 8); else SOMI_SKINNY(16, 4);
-        case 32: if (deep_ring) SOMI_SKINNY(32, 8); else SOMI_SKINNY(32, 4);
+        case 16: if (deep_ring) SOMI_SKINNY(16, 8); else SOMI_SKINNY(16, 6);
+        case 32: if (deep_ring) SOMI_SKINNY(32, 8); else SOMI_SKINNY(32, 5);
         case 64: if (deep_ring) SOMI_SKINNY(64, 8); else SOMI_SKINNY(64, 4);
         default: return SOMI_ERR_UNSUPPORTED;
     }

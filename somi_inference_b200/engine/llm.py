@@ -115,6 +115,8 @@ class LLM:
             self.d2h_bytes_last = host.numel() * host.element_size()
             sampled = {r.request_id: int(t) for r, t in zip(samplers, host.tolist())}
         self.steps_run += 1
+        if self.steps_run % 256 == 0 and hasattr(self.engine.ops, "check_errors"):
+            self.engine.ops.check_errors()
         return self.scheduler.update(batch, sampled)
 
     def run(self, requests: Sequence[tuple[int, Request]]) -> list[Request]:

@@ -55,6 +55,7 @@ def main(argv: list[str] | None = None) -> int:
             if logits.shape[0]:
                 logits.detach().to("cpu").contiguous().numpy().astype("<f4").tofile(
                     os.path.join(args.out, f"{step}.f32"))
+            engine.ops.check_errors()       # a kernel that gave up on a bounded wait says so here
         for rid in rec.get("end", []):
             if engine.has(rid):
                 engine.end(rid)

@@ -28,6 +28,9 @@ class HostOps:
     def skinny_supported(self, M, N, K, dtype) -> bool:
         return False
 
+    def check_errors(self) -> None:
+        pass
+
     def add_rmsnorm(self, residual, delta, weight, eps, out, rows=None) -> None:
         if delta is not None and delta.dim() == 3:
             delta = delta.sum(0)
