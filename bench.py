@@ -24,7 +24,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SHAPES = {
-    # BASELINE.json configs[2], [3], [4]
+    # the three benchmark shapes: Qwen2.5-0.5B, 7B and 14B sizes
     "0.5b": dict(num_hidden_layers=24, hidden_size=896, num_attention_heads=14,
                  num_key_value_heads=2, head_dim=64, intermediate_size=4864, vocab_size=151936,
                  rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=True),
