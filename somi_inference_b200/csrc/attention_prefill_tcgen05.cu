@@ -1,0 +1,385 @@
+// Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
+//
+// One CTA = up to 128 consecutive query rows of one request x one query head; key tiles of 128
+// positions aligned to multiples of 128.  Both products run as `tcgen05.mma` with accumulators
+// in tensor memory: S = Q K^T (128 x 128, two buffers so that the next tile's scores are
+// computed while this tile's softmax runs) and PV = P V (128 x head_dim).  Operands come from
+// shared memory in the 128-byte-swizzle layout: Q and the K/V pages by `cp.async.bulk.tensor.2d`
+// (V is the MN-major operand of the second product, so the cache's [key][dim] rows are used as
+// they are), P written by the softmax warps.  Warp roles: warp 0 producer (TMA), warp 1 MMA
+// issuer, warps 2-5 softmax: each of their 128 threads owns one query row (one lane of tensor
+// memory), so row maximum and row sum need no shuffles; the running output stays in registers
+// and is corrected by exp2(m_old - m_new) when a tile's product is added.  Softmax is float32,
+// base 2.  Every wait on an mbarrier is bounded and failure is recorded in an error word.
+//
+// The reference's prefill kernel (somi_inference/core/flash_attention_triton.py:31-194) is a
+// FlashAttention-2 loop on `tl.dot`; formulas in somi_inference/models/qwen2.py:158-186.
+#include "mma.cuh"
+#include "tma.cuh"
+
+namespace somi {
+
+constexpr int kFaBM = 128;
+constexpr int kFaBN = 128;
+constexpr int kFaThreads = 192;
+constexpr int kFaHalf = 128 * 128;          // bytes of one [128 rows][64 elements] swizzled block
+
+__device__ int g_prefill_tc_error = 0;
+
+__device__ __forceinline__ uint64_t fa_desc_kmajor(uint32_t addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+// MN-major operand: 64 elements (128 bytes) contiguous along N, 8 K-rows form a 1024-byte
+// group; the leading byte offset steps to the next 64-element block along N, the stride byte
+// offset to the next group of 8 rows along K.
+__device__ __forceinline__ uint64_t fa_desc_mnmajor(uint32_t addr, uint32_t lbo_bytes) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+__device__ __forceinline__ void fa_umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void fa_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fa_tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+}
+__device__ __forceinline__ void fa_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void fa_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kFaThreads, 1)
+paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
+                        const __grid_constant__ CUtensorMap kv_map, long long k_row0,
+                        long long v_row0, const int* __restrict__ block_table, int bt_stride,
+                        const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
+                        const int* __restrict__ tiles, int nq, int nkv, int page_size,
+                        float scale_log2e, int window, __nv_bfloat16* __restrict__ out) {
+    constexpr int HALVES = HD / 64;
+    constexpr int TILE = HALVES * kFaHalf;               // bytes of a Q, K or V tile
+    constexpr uint32_t TmemCols = 512;                   // S0 | S1 | PV (| unused)
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    unsigned char* Qs = base;
+    unsigned char* Ks = Qs + TILE;                       // two stages
+    unsigned char* Vs = Ks + 2 * TILE;                   // two stages
+    unsigned char* Ps = Vs + 2 * TILE;
+    __shared__ __align__(8) unsigned long long q_full, kv_full[2], kv_empty[2], s_full[2], p_full,
+        pv_full;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int failed_s;
+
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        mbar_init(smem_u32(&q_full), 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(smem_u32(&kv_full[s]), 1);
+            mbar_init(smem_u32(&kv_empty[s]), 1);
+            mbar_init(smem_u32(&s_full[s]), 1);
+        }
+        mbar_init(smem_u32(&p_full), 4);                 // one arrival per softmax warp
+        mbar_init(smem_u32(&pv_full), 1);
+        mbar_fence_init();
+        failed_s = 0;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(
+                         smem_u32(&tmem_base_s)),
+                     "r"(TmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    // value rows that no copy fills (pages outside the request's range) must be finite numbers
+    for (int c = tid; c < 2 * TILE / 16; c += kFaThreads)
+        reinterpret_cast<uint4*>(Vs)[c] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async();
+    fa_fence_before();
+    __syncthreads();
+    fa_fence_after();
+    pdl_wait();
+    const uint32_t tmem_s = tmem_base_s;                 // S buffers at columns 0 and 128
+    const uint32_t tmem_pv = tmem_base_s + 256;
+
+    const int req = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1];
+    const int rows = tiles[3 * blockIdx.x + 2];
+    const int head = blockIdx.y, kvh = head / (nq / nkv);
+    const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
+    const int kv_end = q_pos0 + rows;
+    const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;
+    const int kb0 = (kv_first / kFaBN) * kFaBN;
+    const int n_tiles = (kv_end - kb0 + kFaBN - 1) / kFaBN;
+    const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(smem_u32(&q_full), kFaBM * HD * 2);
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+                tma_load_2d(smem_u32(Qs + h * kFaHalf), &q_map, head * HD + h * 64, row0,
+                            smem_u32(&q_full));
+            for (int t = 0; t < n_tiles; ++t) {
+                const int st = t & 1;
+                if (!mbar_wait(smem_u32(&kv_empty[st]), ((t >> 1) & 1) ^ 1)) { failed_s = 1; break; }
+                const int kb = kb0 + t * kFaBN;
+                const int p_lo = max(kb, kv_first) / page_size;
+                const int p_hi = (min(kb + kFaBN, kv_end) - 1) / page_size;
+                const uint32_t bar = smem_u32(&kv_full[st]);
+                mbar_expect_tx(bar, static_cast<uint32_t>(p_hi - p_lo + 1) * page_size * HD * 2 * 2);
+                for (int ap = p_lo; ap <= p_hi; ++ap) {
+                    const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
+                    const int r = ap * page_size - kb;
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) {
+                        tma_load_2d(smem_u32(Ks + st * TILE + h * kFaHalf + r * 128), &kv_map, h * 64,
+                                    static_cast<int>(k_row0 + prow), bar);
+                        tma_load_2d(smem_u32(Vs + st * TILE + h * kFaHalf + r * 128), &kv_map, h * 64,
+                                    static_cast<int>(v_row0 + prow), bar);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // float32 accumulators, bf16 operands; scores: both K-major, N = 128 keys;
+            // P.V: A (P) K-major, B (V) MN-major, N = head_dim
+            const uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) |
+                                      (static_cast<uint32_t>(kFaBN >> 3) << 17) |
+                                      (static_cast<uint32_t>(kFaBM >> 4) << 24);
+            const uint32_t idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                      (static_cast<uint32_t>(HD >> 3) << 17) |
+                                      (static_cast<uint32_t>(kFaBM >> 4) << 24);
+            bool ok = mbar_wait(smem_u32(&q_full), 0);
+            auto issue_scores = [&](int t) {
+                const int st = t & 1;
+                if (!mbar_wait(smem_u32(&kv_full[st]), (t >> 1) & 1)) { ok = false; return; }
+                fa_fence_after();
+                const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + st * TILE);
+#pragma unroll
+                for (int k16 = 0; k16 < HD / 16; ++k16) {
+                    const uint32_t o = (k16 >> 2) * kFaHalf + (k16 & 3) * 32;
+                    fa_umma(tmem_s + (t & 1) * kFaBN, fa_desc_kmajor(qa + o), fa_desc_kmajor(ka + o),
+                            idesc_qk, k16 > 0 ? 1u : 0u);
+                }
+                fa_commit(smem_u32(&s_full[t & 1]));
+            };
+            if (ok) issue_scores(0);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                if (t + 1 < n_tiles) issue_scores(t + 1);      // overlaps this tile's softmax
+                if (!ok) break;
+                if (!mbar_wait(smem_u32(&p_full), t & 1)) { ok = false; break; }
+                fa_fence_after();
+                const int st = t & 1;
+                const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs + st * TILE);
+#pragma unroll
+                for (int k16 = 0; k16 < kFaBN / 16; ++k16) {
+                    const uint32_t po = (k16 >> 2) * kFaHalf + (k16 & 3) * 32;
+                    fa_umma(tmem_pv, fa_desc_kmajor(pa + po),
+                            fa_desc_mnmajor(va + k16 * 16 * 128, kFaHalf), idesc_pv, k16 > 0 ? 1u : 0u);
+                }
+                fa_commit(smem_u32(&pv_full));
+                fa_commit(smem_u32(&kv_empty[st]));
+            }
+            if (!ok) {
+                failed_s = 1;
+                // let the softmax warps run out of their bounded waits instead of hanging
+            }
+        }
+    } else {
+        // ---- softmax warps: thread = one query row = one lane of tensor memory
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
+        const int pos = q_pos0 + row;
+        const int lo = window > 0 ? max(kv_first, pos - window + 1) : kv_first;
+        float o[HD];
+#pragma unroll
+        for (int d = 0; d < HD; ++d) o[d] = 0.f;
+        float m = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int kb = kb0 + t * kFaBN;
+            ok = mbar_wait(smem_u32(&s_full[t & 1]), (t >> 1) & 1, ok ? 400000 : 1) && ok;
+            fa_fence_after();
+            const uint32_t s_addr = tmem_s + (t & 1) * kFaBN + lane_addr;
+            // pass 1: the row's maximum over this tile's visible keys
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < kFaBN / 32; ++c) {
+                float v[32];
+                fa_tmem_ld32(s_addr + c * 32, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int key = kb + c * 32 + j;
+                    if (key <= pos && key >= lo) tmax = fmaxf(tmax, v[j] * scale_log2e);
+                }
+            }
+            const float m_new = fmaxf(m, tmax);
+            const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = fast_exp2(m - m_safe);         // m = -inf gives 0
+            m = m_new;
+            // pass 2: probabilities, rounded to bfloat16, into shared memory (swizzled rows)
+            float psum = 0.f;
+#pragma unroll
+            for (int c = 0; c < kFaBN / 32; ++c) {
+                float v[32];
+                fa_tmem_ld32(s_addr + c * 32, v);
+                uint32_t packed[16];
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    const int key = kb + c * 32 + j;
+                    const float p0 = (key <= pos && key >= lo) ? fast_exp2(v[j] * scale_log2e - m_safe) : 0.f;
+                    const float p1 = (key + 1 <= pos && key + 1 >= lo) ? fast_exp2(v[j + 1] * scale_log2e - m_safe) : 0.f;
+                    const uint32_t pk = pack_bf16(p0, p1);
+                    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&pk);
+                    psum += __low2float(b2) + __high2float(b2);
+                    packed[j >> 1] = pk;
+                }
+                // 32 keys = 64 bytes = chunks 4c' .. 4c'+3 of this row's 128-byte line in block c / 2
+                unsigned char* prow = Ps + (c >> 1) * kFaHalf + row * 128;
+#pragma unroll
+                for (int ch = 0; ch < 4; ++ch) {
+                    const int chunk = (c & 1) * 4 + ch;
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
+                        make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
+                }
+            }
+            l = l * alpha + psum;
+            fa_fence_before();
+            fence_proxy_async();                // P is read by the tensor core (async proxy)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&p_full));
+            // correction: add this tile's P.V to the running output
+            ok = mbar_wait(smem_u32(&pv_full), t & 1, ok ? 400000 : 1) && ok;
+            fa_fence_after();
+#pragma unroll
+            for (int c = 0; c < HD / 32; ++c) {
+                float v[32];
+                fa_tmem_ld32(tmem_pv + lane_addr + c * 32, v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + v[j];
+            }
+            fa_fence_before();
+        }
+        if (!ok) failed_s = 1;
+        if (row < rows) {
+            const float inv = 1.0f / l;
+            __nv_bfloat16* dst = out + static_cast<size_t>(row0 + row) * nq * HD + head * HD;
+#pragma unroll
+            for (int d = 0; d < HD; d += 8) {
+                uint4 w;
+                w.x = pack_bf16(o[d] * inv, o[d + 1] * inv);
+                w.y = pack_bf16(o[d + 2] * inv, o[d + 3] * inv);
+                w.z = pack_bf16(o[d + 4] * inv, o[d + 5] * inv);
+                w.w = pack_bf16(o[d + 6] * inv, o[d + 7] * inv);
+                *reinterpret_cast<uint4*>(dst + d) = w;
+            }
+        }
+    }
+    fa_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base_s),
+                     "r"(TmemCols)
+                     : "memory");
+    }
+    if (tid == 0 && failed_s) atomicExch(&g_prefill_tc_error, 1);
+}
+
+template <int HD>
+int launch_prefill_tc(const CUtensorMap* q_map, const CUtensorMap* kv_map, long long k_row0,
+                      long long v_row0, const int* block_table, int bt_stride, const int* cu_q,
+                      const int* ctx_len, const int* tiles, int n_tiles, int nq, int nkv,
+                      int page_size, float scale, int window, void* out, cudaStream_t stream) {
+    constexpr int TILE = (HD / 64) * kFaHalf;
+    const size_t smem = 5 * TILE + 2 * kFaHalf + 1024;
+    cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         (int)smem);
+    dim3 grid(n_tiles, nq);
+    launch_pdl(paged_prefill_tc_kernel<HD>, grid, dim3(kFaThreads), smem, stream, *q_map, *kv_map,
+               k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len, tiles, nq, nkv, page_size,
+               scale * 1.4426950408889634f, window, static_cast<__nv_bfloat16*>(out));
+    return launch_status();
+}
+
+}  // namespace somi
+
+using namespace somi;
+
+SOMI_API int somi_prefill_tc_q_tile() { return kFaBM; }
+
+SOMI_API int somi_prefill_tc_supported(int nq, int nkv, int hd, int page_size) {
+    if (nkv <= 0 || nq % nkv) return 0;
+    if (hd != 64 && hd != 128) return 0;
+    return page_size >= 8 && page_size % 8 == 0 && kFaBN % page_size == 0;
+}
+
+SOMI_API int somi_prefill_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_prefill_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_prefill_tc_error, &zero, sizeof(int));
+    return v;
+}
+
+// A tensor map over the step's projection buffer [tokens, width] (bfloat16, row-major) with
+// boxes of 128 rows x 64 columns, from which the query tiles are fetched.
+SOMI_API int somi_make_q_tensor_map(void* map_out, const void* qkv, long long tokens,
+                                    long long width) {
+    if (width % 8 != 0) return SOMI_ERR_UNSUPPORTED;
+    return make_tensor_map_bf16_2d(static_cast<CUtensorMap*>(map_out), qkv,
+                                   static_cast<uint64_t>(tokens), static_cast<uint64_t>(width),
+                                   kFaBM, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// `tiles`: int32 [n_tiles, 3] = (request, first row, rows <= 128) over the multi-token requests.
+SOMI_API int somi_paged_attention_prefill_tc(
+    const void* q_map, const void* kv_map, long long k_row0, long long v_row0,
+    const int* block_table, int bt_stride, const int* cu_q, const int* ctx_len, const int* tiles,
+    int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, void* out,
+    cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (!somi_prefill_tc_supported(nq, nkv, hd, page_size) || nq > 65535) return SOMI_ERR_UNSUPPORTED;
+    const CUtensorMap* qm = static_cast<const CUtensorMap*>(q_map);
+    const CUtensorMap* km = static_cast<const CUtensorMap*>(kv_map);
+    if (hd == 64)
+        return launch_prefill_tc<64>(qm, km, k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len,
+                                     tiles, n_tiles, nq, nkv, page_size, scale, window, out, stream);
+    return launch_prefill_tc<128>(qm, km, k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len, tiles,
+                                  n_tiles, nq, nkv, page_size, scale, window, out, stream);
+}

@@ -102,6 +102,7 @@ class BatchBuilder:
         self._event_pool = [torch.cuda.Event(), torch.cuda.Event()] if pin else [None, None]
         self._dev = torch.empty(capacity, dtype=torch.int32, device=self.device)
         self._capacity = capacity
+        self.generation = getattr(self, "generation", 0) + 1    # device addresses changed
 
     @property
     def h2d_bytes_last(self) -> int:

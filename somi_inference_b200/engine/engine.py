@@ -95,6 +95,7 @@ class Engine:
         self._graphs: dict[tuple, tuple] = {}
         self._seen: dict[tuple, int] = {}
         self._graph_pool = None
+        self._graph_generation = self.builder.generation
 
     # ------------------------------------------------------------------ step
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
@@ -147,6 +148,11 @@ class Engine:
         if not graphable:
             with torch.no_grad():
                 return self.model.forward(batch, self.cache)
+        if self._graph_generation != self.builder.generation:
+            # the descriptor buffer moved: graphs captured over the old addresses are void
+            self._graphs.clear()
+            self._seen.clear()
+            self._graph_generation = self.builder.generation
         key = batch.layout_key
         entry = self._graphs.get(key)
         if entry is not None:

@@ -61,7 +61,11 @@ class CudaOps:
         self.generic_q_tile = int(self.lib.somi_attention_generic_q_tile())
         self.lib.somi_prefill_q_tile.restype = ctypes.c_int
         self.prefill_q_tile = int(self.lib.somi_prefill_q_tile())
-        self.q_tile_sizes = (self.generic_q_tile, self.prefill_q_tile)
+        self.lib.somi_prefill_tc_q_tile.restype = ctypes.c_int
+        self.prefill_tc_q_tile = int(self.lib.somi_prefill_tc_q_tile())
+        self.q_tile_sizes = (self.generic_q_tile, self.prefill_q_tile, self.prefill_tc_q_tile)
+        self.use_tc_prefill = True
+        self._q_maps: dict = {}
         self.lib.somi_decode_chunk.restype = ctypes.c_int
         self.decode_chunk = int(self.lib.somi_decode_chunk())
         self._workspace = None
@@ -193,6 +197,23 @@ class CudaOps:
         """Programmatic dependent launch for all kernels of the library (on by default)."""
         self.lib.somi_set_pdl(ctypes.c_int(1 if on else 0))
 
+    def _q_tensor_map(self, qkv: torch.Tensor) -> int:
+        key = (qkv.data_ptr(), qkv.shape[0], qkv.shape[1])
+        entry = self._q_maps.get(key)
+        if entry is None:
+            if len(self._q_maps) > 4096:
+                self._q_maps.clear()
+            raw = (ctypes.c_ubyte * 256)()
+            addr = (ctypes.addressof(raw) + 127) & ~127
+            rc = self.lib.somi_make_q_tensor_map(ctypes.c_void_p(addr), _ptr(qkv),
+                                                 ctypes.c_longlong(qkv.shape[0]),
+                                                 ctypes.c_longlong(qkv.shape[1]))
+            if rc != 0:
+                raise KernelError(f"could not encode a tensor map over the projection buffer (code {rc})")
+            entry = (raw, addr)
+            self._q_maps[key] = entry
+        return entry[1]
+
     def check_errors(self) -> None:
         """Raise if a kernel recorded that one of its bounded waits ran out (synchronises)."""
         if int(self.lib.somi_decode_tma_error()) != 0:
@@ -200,6 +221,9 @@ class CudaOps:
                               "its results are not valid")
         if int(self.lib.somi_prefill_tma_error()) != 0:
             raise KernelError("the TMA prefill attention kernel gave up waiting for a copy; "
+                              "its results are not valid")
+        if int(self.lib.somi_prefill_tc_error()) != 0:
+            raise KernelError("the tcgen05 prefill attention kernel gave up waiting on a barrier; "
                               "its results are not valid")
         if int(self.lib.somi_gemm_error()) != 0:
             raise KernelError("the tcgen05 matrix product gave up waiting on a barrier; "
@@ -226,7 +250,27 @@ class CudaOps:
             tma = (self.use_tma_prefill and storage is not None and bool(
                 self.lib.somi_prefill_tma_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
                                                     ctypes.c_int(hd), ctypes.c_int(page_size))))
-            if tma:
+            tc = (self.use_tc_prefill and storage is not None and qkv.shape[1] % 8 == 0 and bool(
+                self.lib.somi_prefill_tc_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
+                                                   ctypes.c_int(hd), ctypes.c_int(page_size))))
+            if tc:
+                # both products on tcgen05 tensor cores, accumulators in tensor memory
+                tiles = batch.tiles[self.prefill_tc_q_tile]
+                row_bytes = hd * 2
+                rc = self.lib.somi_paged_attention_prefill_tc(
+                    ctypes.c_void_p(self._q_tensor_map(qkv)),
+                    ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)),
+                    ctypes.c_longlong((kcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    ctypes.c_longlong((vcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
+                    ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
+                    ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
+                self._done(rc, "paged_attention_prefill_tc")
+                tma = None
+            if tma is None:
+                pass
+            elif tma:
                 row_bytes = hd * 2
                 rc = self.lib.somi_paged_attention_prefill_tma(
                     ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)), _ptr(qkv),
@@ -244,7 +288,8 @@ class CudaOps:
                     _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
                     ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
                     ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
-            self._done(rc, "paged_attention_prefill")
+            if tma is not None:
+                self._done(rc, "paged_attention_prefill")
         tiles = batch.tiles[self.generic_q_tile]
         n_generic_tiles = 0 if tensor_core_prefill else tiles.shape[0]
         n_generic_decode = 0 if split else n_decode

@@ -15,7 +15,7 @@ import torch
 class HostOps:
     name = "host"
     generic_q_tile = 16
-    q_tile_sizes = (16, 64)
+    q_tile_sizes = (16, 64, 128)
     launches = 0
 
     def check_attention_geometry(self, num_heads, num_kv_heads, head_dim) -> None:

@@ -226,9 +226,9 @@ PREFILL_CASES = [
 ]
 
 
-@pytest.mark.parametrize("tma", [True, False], ids=["tma", "cp_async"])
+@pytest.mark.parametrize("path", ["tcgen05", "tma", "cp_async"])
 @pytest.mark.parametrize("case", PREFILL_CASES, ids=[f"p{i}" for i in range(len(PREFILL_CASES))])
-def test_tensor_core_prefill_attention(ops, case, tma):
+def test_tensor_core_prefill_attention(ops, case, path):
     """Portions with and without cached context, around the 64-row and 64-key tile edges,
     windows shorter and longer than a tile; bfloat16 goes through the tensor-core kernel."""
     nq, nkv, hd, ps, window, reqs = case
@@ -237,13 +237,14 @@ def test_tensor_core_prefill_attention(ops, case, tma):
                                               window=window, requests=reqs, dtype=torch.bfloat16,
                                               seed=11)
     out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
-    ops.use_tma_prefill = tma
+    ops.use_tc_prefill = path == "tcgen05"
+    ops.use_tma_prefill = path != "cp_async"
     try:
         ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
                             hd ** -0.5, window, out, storage=view.storage)
         ops.check_errors()
     finally:
-        ops.use_tma_prefill = True
+        ops.use_tma_prefill = ops.use_tc_prefill = True
     ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
     cb = batch_to_cpu(batch)
     HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), cb, cb.groups[0], nq, nkv,
