@@ -7,10 +7,12 @@
 // shared memory in the 128-byte-swizzle layout: Q and the K/V pages by `cp.async.bulk.tensor.2d`
 // (V is the MN-major operand of the second product, so the cache's [key][dim] rows are used as
 // they are), P written by the softmax warps.  Warp roles: warp 0 producer (TMA), warp 1 MMA
-// issuer, warps 2-5 softmax: each of their 128 threads owns one query row (one lane of tensor
-// memory), so row maximum and row sum need no shuffles; the running output stays in registers
-// and is corrected by exp2(m_old - m_new) when a tile's product is added.  Softmax is float32,
-// base 2.  Every wait on an mbarrier is bounded and failure is recorded in an error word.
+// issuer, warps 2-9 softmax: a query row is one lane of tensor memory and is served by two
+// threads (one per 64 of a tile's 128 keys) that agree on the row maximum through shared memory.  The output accumulates in tensor
+// memory across key tiles; it is rescaled there (tcgen05.ld / tcgen05.st) only when a row's
+// maximum grows by more than 2^8, otherwise the old maximum keeps serving as the reference
+// (probabilities up to 256 are harmless in float32 sums and bfloat16 operands), so most tiles
+// cost the softmax warps one pass over S and one over P.  Softmax is float32, base 2.  Every wait on an mbarrier is bounded and failure is recorded in an error word.
 //
 // The reference's prefill kernel (somi_inference/core/flash_attention_triton.py:31-194) is a
 // FlashAttention-2 loop on `tl.dot`; formulas in somi_inference/models/qwen2.py:158-186.
@@ -21,7 +23,7 @@ namespace somi {
 
 constexpr int kFaBM = 128;
 constexpr int kFaBN = 128;
-constexpr int kFaThreads = 192;
+constexpr int kFaThreads = 320;          // producer warp, MMA warp, 8 softmax warps
 constexpr int kFaHalf = 128 * 128;          // bytes of one [128 rows][64 elements] swizzled block
 
 __device__ int g_prefill_tc_error = 0;
@@ -75,6 +77,35 @@ __device__ __forceinline__ void fa_tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
 }
+// The same without waiting: several loads may be in flight before one fa_tmem_wait_ld().
+__device__ __forceinline__ void fa_tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void fa_tmem_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void fa_pair_sync(int id) {          // the two warps that share rows
+    asm volatile("bar.sync %0, 64;\n" ::"r"(id) : "memory");
+}
+__device__ __forceinline__ void fa_tmem_st32(uint32_t taddr, const float (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n" ::"r"(taddr),
+        "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]),
+        "f"(v[8]), "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]),
+        "f"(v[16]), "f"(v[17]), "f"(v[18]), "f"(v[19]), "f"(v[20]), "f"(v[21]), "f"(v[22]),
+        "f"(v[23]), "f"(v[24]), "f"(v[25]), "f"(v[26]), "f"(v[27]), "f"(v[28]), "f"(v[29]),
+        "f"(v[30]), "f"(v[31])
+        : "memory");
+}
 __device__ __forceinline__ void fa_fence_before() {
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
 }
@@ -99,11 +130,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     unsigned char* Qs = base;
     unsigned char* Ks = Qs + TILE;                       // two stages
     unsigned char* Vs = Ks + 2 * TILE;                   // two stages
-    unsigned char* Ps = Vs + 2 * TILE;
-    __shared__ __align__(8) unsigned long long q_full, kv_full[2], kv_empty[2], s_full[2], p_full,
-        pv_full;
+    unsigned char* Ps = Vs + 2 * TILE;                   // two buffers of 128 rows x 128 keys
+    __shared__ __align__(8) unsigned long long q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2],
+        pv_full[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
+    __shared__ float xmax_s[2][kFaBM];       // exchanged between the two warps that share a row
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -113,9 +145,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             mbar_init(smem_u32(&kv_full[s]), 1);
             mbar_init(smem_u32(&kv_empty[s]), 1);
             mbar_init(smem_u32(&s_full[s]), 1);
+            mbar_init(smem_u32(&p_full[s]), 8);          // one arrival per softmax warp
+            mbar_init(smem_u32(&pv_full[s]), 1);
         }
-        mbar_init(smem_u32(&p_full), 4);                 // one arrival per softmax warp
-        mbar_init(smem_u32(&pv_full), 1);
         mbar_fence_init();
         failed_s = 0;
     }
@@ -148,30 +180,43 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
 
     if (warp == 0) {
+        // producer warp: lane 0 keeps the barriers, one lane per page looks its page up and
+        // issues that page's copies, so the page-table reads of a tile run side by side
         if (lane == 0) {
             mbar_expect_tx(smem_u32(&q_full), kFaBM * HD * 2);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
                 tma_load_2d(smem_u32(Qs + h * kFaHalf), &q_map, head * HD + h * 64, row0,
                             smem_u32(&q_full));
-            for (int t = 0; t < n_tiles; ++t) {
-                const int st = t & 1;
-                if (!mbar_wait(smem_u32(&kv_empty[st]), ((t >> 1) & 1) ^ 1)) { failed_s = 1; break; }
-                const int kb = kb0 + t * kFaBN;
-                const int p_lo = max(kb, kv_first) / page_size;
-                const int p_hi = (min(kb + kFaBN, kv_end) - 1) / page_size;
-                const uint32_t bar = smem_u32(&kv_full[st]);
-                mbar_expect_tx(bar, static_cast<uint32_t>(p_hi - p_lo + 1) * page_size * HD * 2 * 2);
-                for (int ap = p_lo; ap <= p_hi; ++ap) {
-                    const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
-                    const int r = ap * page_size - kb;
+        }
+        const int pages_per_tile = kFaBN / page_size;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int st = t & 1;
+            const int kb = kb0 + t * kFaBN;
+            const int p_lo = max(kb, kv_first) / page_size;
+            const int p_hi = (min(kb + kFaBN, kv_end) - 1) / page_size;
+            // the table entries do not depend on the stage being free: read them first
+            int my_page = -1;
+            const int ap = kb / page_size + lane;
+            if (lane < pages_per_tile && ap >= p_lo && ap <= p_hi) my_page = bt[ap];
+            const uint32_t bar = smem_u32(&kv_full[st]);
+            int ok = 1;
+            if (lane == 0) {
+                ok = mbar_wait(smem_u32(&kv_empty[st]), ((t >> 1) & 1) ^ 1) ? 1 : 0;
+                if (ok) mbar_expect_tx(bar, static_cast<uint32_t>(p_hi - p_lo + 1) * page_size * HD * 2 * 2);
+                else failed_s = 1;
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (my_page >= 0) {
+                const long long prow = (static_cast<long long>(my_page) * nkv + kvh) * page_size;
+                const int r = lane * page_size;
 #pragma unroll
-                    for (int h = 0; h < HALVES; ++h) {
-                        tma_load_2d(smem_u32(Ks + st * TILE + h * kFaHalf + r * 128), &kv_map, h * 64,
-                                    static_cast<int>(k_row0 + prow), bar);
-                        tma_load_2d(smem_u32(Vs + st * TILE + h * kFaHalf + r * 128), &kv_map, h * 64,
-                                    static_cast<int>(v_row0 + prow), bar);
-                    }
+                for (int h = 0; h < HALVES; ++h) {
+                    tma_load_2d(smem_u32(Ks + st * TILE + h * kFaHalf + r * 128), &kv_map, h * 64,
+                                static_cast<int>(k_row0 + prow), bar);
+                    tma_load_2d(smem_u32(Vs + st * TILE + h * kFaHalf + r * 128), &kv_map, h * 64,
+                                static_cast<int>(v_row0 + prow), bar);
                 }
             }
         }
@@ -203,17 +248,18 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             for (int t = 0; t < n_tiles && ok; ++t) {
                 if (t + 1 < n_tiles) issue_scores(t + 1);      // overlaps this tile's softmax
                 if (!ok) break;
-                if (!mbar_wait(smem_u32(&p_full), t & 1)) { ok = false; break; }
+                if (!mbar_wait(smem_u32(&p_full[t & 1]), (t >> 1) & 1)) { ok = false; break; }
                 fa_fence_after();
                 const int st = t & 1;
-                const uint32_t pa = smem_u32(Ps), va = smem_u32(Vs + st * TILE);
+                const uint32_t pa = smem_u32(Ps + (t & 1) * 2 * kFaHalf), va = smem_u32(Vs + st * TILE);
 #pragma unroll
                 for (int k16 = 0; k16 < kFaBN / 16; ++k16) {
                     const uint32_t po = (k16 >> 2) * kFaHalf + (k16 & 3) * 32;
                     fa_umma(tmem_pv, fa_desc_kmajor(pa + po),
-                            fa_desc_mnmajor(va + k16 * 16 * 128, kFaHalf), idesc_pv, k16 > 0 ? 1u : 0u);
+                            fa_desc_mnmajor(va + k16 * 16 * 128, kFaHalf), idesc_pv,
+                            (t > 0 || k16 > 0) ? 1u : 0u);     // O accumulates over the key tiles
                 }
-                fa_commit(smem_u32(&pv_full));
+                fa_commit(smem_u32(&pv_full[t & 1]));
                 fa_commit(smem_u32(&kv_empty[st]));
             }
             if (!ok) {
@@ -222,93 +268,114 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             }
         }
     } else {
-        // ---- softmax warps: thread = one query row = one lane of tensor memory
-        const int q = warp & 3;
+        // ---- softmax warps: a query row (one lane of tensor memory) is shared by two threads,
+        // one per half of the tile's 128 keys; they agree on the row maximum through shared memory
+        const int q = warp & 3;                                  // lane quarter this warp may access
+        const int half = (warp - 2) >> 2;                        // which 64 keys of a tile
         const int row = q * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const int pos = q_pos0 + row;
         const int lo = window > 0 ? max(kv_first, pos - window + 1) : kv_first;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.f;
-        float m = -INFINITY, l = 0.f;
+        float m = -INFINITY, l = 0.f;        // m: the reference maximum in use (log2 units)
         bool ok = true;
         for (int t = 0; t < n_tiles; ++t) {
-            const int kb = kb0 + t * kFaBN;
+            const int kb = kb0 + t * kFaBN + half * 64;
             ok = mbar_wait(smem_u32(&s_full[t & 1]), (t >> 1) & 1, ok ? 400000 : 1) && ok;
             fa_fence_after();
-            const uint32_t s_addr = tmem_s + (t & 1) * kFaBN + lane_addr;
-            // pass 1: the row's maximum over this tile's visible keys
+            const uint32_t s_addr = tmem_s + (t & 1) * kFaBN + half * 64 + lane_addr;
+            uint32_t raw[64];
+            fa_tmem_ld32_nowait(s_addr, raw);
+            fa_tmem_ld32_nowait(s_addr + 32, raw + 32);
+            fa_tmem_wait_ld();
+            float sv[64];
+            const bool inner = kb + 63 <= pos && kb >= lo;       // no hidden key for this row here
             float tmax = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < kFaBN / 32; ++c) {
-                float v[32];
-                fa_tmem_ld32(s_addr + c * 32, v);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    const int key = kb + c * 32 + j;
-                    if (key <= pos && key >= lo) tmax = fmaxf(tmax, v[j] * scale_log2e);
-                }
+            for (int j = 0; j < 64; ++j) {
+                const int key = kb + j;
+                const float x = (inner || (key <= pos && key >= lo))
+                                    ? __uint_as_float(raw[j]) * scale_log2e : -INFINITY;
+                sv[j] = x;
+                tmax = fmaxf(tmax, x);
             }
-            const float m_new = fmaxf(m, tmax);
-            const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = fast_exp2(m - m_safe);         // m = -inf gives 0
-            m = m_new;
-            // pass 2: probabilities, rounded to bfloat16, into shared memory (swizzled rows)
+            xmax_s[half][row] = tmax;
+            fa_pair_sync(1 + q);
+            tmax = fmaxf(tmax, xmax_s[half ^ 1][row]);
+            // this tile's P buffer was last read by the product of tile t - 2
+            if (t >= 2) ok = mbar_wait(smem_u32(&pv_full[t & 1]), ((t >> 1) - 1) & 1, ok ? 400000 : 1) && ok;
+            // keep the old reference maximum unless the new one is more than 2^8 above it
+            float alpha = 1.f;
+            bool rescale = false;
+            if (m == -INFINITY) {
+                m = tmax;                                   // nothing accumulated yet for this row
+            } else if (tmax > m + 8.0f) {
+                alpha = fast_exp2(m - tmax);
+                m = tmax;
+                rescale = true;
+            }
+            if (__any_sync(0xffffffffu, rescale)) {
+                // O of the tiles so far must be complete before it is rescaled in tensor memory;
+                // each of the two threads of a row rescales one half of the columns
+                if (t >= 1) ok = mbar_wait(smem_u32(&pv_full[(t - 1) & 1]), ((t - 1) >> 1) & 1, ok ? 400000 : 1) && ok;
+                fa_fence_after();
+#pragma unroll
+                for (int c = 0; c < HD / 64; ++c) {
+                    float v[32];
+                    const uint32_t a = tmem_pv + lane_addr + half * (HD / 2) + c * 32;
+                    fa_tmem_ld32(a, v);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] *= alpha;
+                    fa_tmem_st32(a, v);
+                }
+                asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                l *= alpha;
+            }
+            const float neg_m = m == -INFINITY ? 0.f : -m;
             float psum = 0.f;
+            unsigned char* prow = Ps + (t & 1) * 2 * kFaHalf + half * kFaHalf + row * 128;
 #pragma unroll
-            for (int c = 0; c < kFaBN / 32; ++c) {
-                float v[32];
-                fa_tmem_ld32(s_addr + c * 32, v);
-                uint32_t packed[16];
+            for (int ch = 0; ch < 8; ++ch) {
+                uint32_t pk[4];
 #pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    const int key = kb + c * 32 + j;
-                    const float p0 = (key <= pos && key >= lo) ? fast_exp2(v[j] * scale_log2e - m_safe) : 0.f;
-                    const float p1 = (key + 1 <= pos && key + 1 >= lo) ? fast_exp2(v[j + 1] * scale_log2e - m_safe) : 0.f;
-                    const uint32_t pk = pack_bf16(p0, p1);
-                    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&pk);
-                    psum += __low2float(b2) + __high2float(b2);
-                    packed[j >> 1] = pk;
+                for (int j = 0; j < 4; ++j) {
+                    const float p0 = fast_exp2(sv[ch * 8 + 2 * j] + neg_m);
+                    const float p1 = fast_exp2(sv[ch * 8 + 2 * j + 1] + neg_m);
+                    psum += p0 + p1;
+                    pk[j] = pack_bf16(p0, p1);
                 }
-                // 32 keys = 64 bytes = chunks 4c' .. 4c'+3 of this row's 128-byte line in block c / 2
-                unsigned char* prow = Ps + (c >> 1) * kFaHalf + row * 128;
-#pragma unroll
-                for (int ch = 0; ch < 4; ++ch) {
-                    const int chunk = (c & 1) * 4 + ch;
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
-                        make_uint4(packed[4 * ch], packed[4 * ch + 1], packed[4 * ch + 2], packed[4 * ch + 3]);
-                }
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
-            l = l * alpha + psum;
+            l += psum;
             fa_fence_before();
             fence_proxy_async();                // P is read by the tensor core (async proxy)
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&p_full));
-            // correction: add this tile's P.V to the running output
-            ok = mbar_wait(smem_u32(&pv_full), t & 1, ok ? 400000 : 1) && ok;
-            fa_fence_after();
-#pragma unroll
-            for (int c = 0; c < HD / 32; ++c) {
-                float v[32];
-                fa_tmem_ld32(tmem_pv + lane_addr + c * 32, v);
-#pragma unroll
-                for (int j = 0; j < 32; ++j) o[c * 32 + j] = o[c * 32 + j] * alpha + v[j];
-            }
-            fa_fence_before();
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[t & 1]));
         }
+        // ---- the output: O / l from tensor memory; each thread writes half of its row
+        fa_pair_sync(1 + q);             // the partner has read this tile's maximum
+        xmax_s[half][row] = l;
+        fa_pair_sync(1 + q);
+        l += xmax_s[half ^ 1][row];
+        const int last = n_tiles - 1;
+        ok = mbar_wait(smem_u32(&pv_full[last & 1]), (last >> 1) & 1, ok ? 400000 : 1) && ok;
+        fa_fence_after();
         if (!ok) failed_s = 1;
-        if (row < rows) {
-            const float inv = 1.0f / l;
-            __nv_bfloat16* dst = out + static_cast<size_t>(row0 + row) * nq * HD + head * HD;
+        const float inv = 1.0f / l;
+        __nv_bfloat16* dst = out + static_cast<size_t>(row0 + row) * nq * HD + head * HD + half * (HD / 2);
 #pragma unroll
-            for (int d = 0; d < HD; d += 8) {
-                uint4 w;
-                w.x = pack_bf16(o[d] * inv, o[d + 1] * inv);
-                w.y = pack_bf16(o[d + 2] * inv, o[d + 3] * inv);
-                w.z = pack_bf16(o[d + 4] * inv, o[d + 5] * inv);
-                w.w = pack_bf16(o[d + 6] * inv, o[d + 7] * inv);
-                *reinterpret_cast<uint4*>(dst + d) = w;
+        for (int c = 0; c < HD / 64; ++c) {
+            float v[32];
+            fa_tmem_ld32(tmem_pv + lane_addr + half * (HD / 2) + c * 32, v);
+            if (row < rows) {
+#pragma unroll
+                for (int d = 0; d < 32; d += 8) {
+                    uint4 w;
+                    w.x = pack_bf16(v[d] * inv, v[d + 1] * inv);
+                    w.y = pack_bf16(v[d + 2] * inv, v[d + 3] * inv);
+                    w.z = pack_bf16(v[d + 4] * inv, v[d + 5] * inv);
+                    w.w = pack_bf16(v[d + 6] * inv, v[d + 7] * inv);
+                    *reinterpret_cast<uint4*>(dst + c * 32 + d) = w;
+                }
             }
         }
     }
@@ -328,7 +395,7 @@ int launch_prefill_tc(const CUtensorMap* q_map, const CUtensorMap* kv_map, long 
                       const int* ctx_len, const int* tiles, int n_tiles, int nq, int nkv,
                       int page_size, float scale, int window, void* out, cudaStream_t stream) {
     constexpr int TILE = (HD / 64) * kFaHalf;
-    const size_t smem = 5 * TILE + 2 * kFaHalf + 1024;
+    const size_t smem = 5 * TILE + 4 * kFaHalf + 1024;
     cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
     dim3 grid(n_tiles, nq);
