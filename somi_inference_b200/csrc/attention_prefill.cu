@@ -61,8 +61,11 @@ paged_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     pdl_launch_dependents();
     pdl_wait();
 
-    const int req = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1];
-    const int rows = tiles[3 * blockIdx.x + 2];
+    // later tiles of a prompt see more keys: they are started first so that the last CTAs
+    // to run are the short ones
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int req = tiles[3 * tile], row0 = tiles[3 * tile + 1];
+    const int rows = tiles[3 * tile + 2];
     const int head = blockIdx.y, kvh = head / (nq / nkv);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);

@@ -1,9 +1,9 @@
 // Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
 //
-// One CTA = up to 128 consecutive query rows of one request x one query head; key tiles of 128
-// positions aligned to multiples of 128.  Both products run as `tcgen05.mma` with accumulators
-// in tensor memory: S = Q K^T (128 x 128, two buffers so that the next tile's scores are
-// computed while this tile's softmax runs) and PV = P V (128 x head_dim).  Operands come from
+// One CTA = up to 128 consecutive query rows of one request x one query head; key tiles of 64
+// positions aligned to multiples of 64, four of them in flight.  Both products run as
+// `tcgen05.mma` with accumulators in tensor memory: S = Q K^T (128 x 64, two buffers so that the
+// next tile's scores are computed while this tile's softmax runs) and O += P V (128 x head_dim).  Operands come from
 // shared memory in the 128-byte-swizzle layout: Q and the K/V pages by `cp.async.bulk.tensor.2d`
 // (V is the MN-major operand of the second product, so the cache's [key][dim] rows are used as
 // they are), P written by the softmax warps.  Warp roles: warp 0 producer (TMA), warp 1 MMA
@@ -21,10 +21,13 @@
 
 namespace somi {
 
-constexpr int kFaBM = 128;
-constexpr int kFaBN = 128;
+constexpr int kFaBM = 128;               // query rows per CTA
+constexpr int kFaBN = 64;                // keys per tile
+constexpr int kFaStages = 4;             // key/value tiles in flight: a tile's copies take longer
+                                         // than a tile's arithmetic, so several must overlap
 constexpr int kFaThreads = 320;          // producer warp, MMA warp, 8 softmax warps
-constexpr int kFaHalf = 128 * 128;          // bytes of one [128 rows][64 elements] swizzled block
+constexpr int kFaHalf = kFaBM * 128;     // bytes of one [128 rows][64 elements] swizzled block (Q, P)
+constexpr int kFaKvHalf = kFaBN * 128;   // bytes of one [64 keys][64 elements] block (K, V)
 
 __device__ int g_prefill_tc_error = 0;
 
@@ -122,17 +125,18 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                         const int* __restrict__ tiles, int nq, int nkv, int page_size,
                         float scale_log2e, int window, __nv_bfloat16* __restrict__ out) {
     constexpr int HALVES = HD / 64;
-    constexpr int TILE = HALVES * kFaHalf;               // bytes of a Q, K or V tile
-    constexpr uint32_t TmemCols = 512;                   // S0 | S1 | PV (| unused)
+    constexpr int QTILE = HALVES * kFaHalf;              // bytes of the Q tile
+    constexpr int TILE = HALVES * kFaKvHalf;             // bytes of a K or V tile
+    constexpr uint32_t TmemCols = 256;                   // S0 | S1 (64 each) | PV (up to 128)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* Qs = base;
-    unsigned char* Ks = Qs + TILE;                       // two stages
-    unsigned char* Vs = Ks + 2 * TILE;                   // two stages
-    unsigned char* Ps = Vs + 2 * TILE;                   // two buffers of 128 rows x 128 keys
-    __shared__ __align__(8) unsigned long long q_full, kv_full[2], kv_empty[2], s_full[2], p_full[2],
-        pv_full[2];
+    unsigned char* Ks = Qs + QTILE;                      // kFaStages tiles
+    unsigned char* Vs = Ks + kFaStages * TILE;           // kFaStages tiles
+    unsigned char* Ps = Vs + kFaStages * TILE;           // two buffers of 128 rows x 64 keys
+    __shared__ __align__(8) unsigned long long q_full, kv_full[kFaStages], kv_empty[kFaStages],
+        s_full[2], p_full[2], pv_full[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
     __shared__ float xmax_s[2][kFaBM];       // exchanged between the two warps that share a row
@@ -141,9 +145,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         mbar_init(smem_u32(&q_full), 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kFaStages; ++s) {
             mbar_init(smem_u32(&kv_full[s]), 1);
             mbar_init(smem_u32(&kv_empty[s]), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);
             mbar_init(smem_u32(&p_full[s]), 8);          // one arrival per softmax warp
             mbar_init(smem_u32(&pv_full[s]), 1);
@@ -159,18 +165,21 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     // value rows that no copy fills (pages outside the request's range) must be finite numbers
-    for (int c = tid; c < 2 * TILE / 16; c += kFaThreads)
+    for (int c = tid; c < kFaStages * TILE / 16; c += kFaThreads)
         reinterpret_cast<uint4*>(Vs)[c] = make_uint4(0, 0, 0, 0);
     fence_proxy_async();
     fa_fence_before();
     __syncthreads();
     fa_fence_after();
     pdl_wait();
-    const uint32_t tmem_s = tmem_base_s;                 // S buffers at columns 0 and 128
-    const uint32_t tmem_pv = tmem_base_s + 256;
+    const uint32_t tmem_s = tmem_base_s;                 // S buffers at columns 0 and 64
+    const uint32_t tmem_pv = tmem_base_s + 128;
 
-    const int req = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1];
-    const int rows = tiles[3 * blockIdx.x + 2];
+    // later tiles of a prompt see more keys: they are started first so that the last CTAs
+    // to run are the short ones
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int req = tiles[3 * tile], row0 = tiles[3 * tile + 1];
+    const int rows = tiles[3 * tile + 2];
     const int head = blockIdx.y, kvh = head / (nq / nkv);
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
     const int kv_end = q_pos0 + rows;
@@ -191,7 +200,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
         const int pages_per_tile = kFaBN / page_size;
         for (int t = 0; t < n_tiles; ++t) {
-            const int st = t & 1;
+            const int st = t % kFaStages;
             const int kb = kb0 + t * kFaBN;
             const int p_lo = max(kb, kv_first) / page_size;
             const int p_hi = (min(kb + kFaBN, kv_end) - 1) / page_size;
@@ -202,7 +211,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             const uint32_t bar = smem_u32(&kv_full[st]);
             int ok = 1;
             if (lane == 0) {
-                ok = mbar_wait(smem_u32(&kv_empty[st]), ((t >> 1) & 1) ^ 1) ? 1 : 0;
+                ok = mbar_wait(smem_u32(&kv_empty[st]), ((t / kFaStages) & 1) ^ 1) ? 1 : 0;
                 if (ok) mbar_expect_tx(bar, static_cast<uint32_t>(p_hi - p_lo + 1) * page_size * HD * 2 * 2);
                 else failed_s = 1;
             }
@@ -213,9 +222,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 const int r = lane * page_size;
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(smem_u32(Ks + st * TILE + h * kFaHalf + r * 128), &kv_map, h * 64,
+                    tma_load_2d(smem_u32(Ks + st * TILE + h * kFaKvHalf + r * 128), &kv_map, h * 64,
                                 static_cast<int>(k_row0 + prow), bar);
-                    tma_load_2d(smem_u32(Vs + st * TILE + h * kFaHalf + r * 128), &kv_map, h * 64,
+                    tma_load_2d(smem_u32(Vs + st * TILE + h * kFaKvHalf + r * 128), &kv_map, h * 64,
                                 static_cast<int>(v_row0 + prow), bar);
                 }
             }
@@ -231,36 +240,42 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                                       (static_cast<uint32_t>(HD >> 3) << 17) |
                                       (static_cast<uint32_t>(kFaBM >> 4) << 24);
             bool ok = mbar_wait(smem_u32(&q_full), 0);
+            // descriptors differ only in their start address field (units of 16 bytes), so they
+            // are built once and advanced by additions while MMAs are issued
+            const uint64_t q_desc = fa_desc_kmajor(smem_u32(Qs));
+            const uint64_t k_desc = fa_desc_kmajor(smem_u32(Ks));
+            const uint64_t p_desc = fa_desc_kmajor(smem_u32(Ps));
+            const uint64_t v_desc = fa_desc_mnmajor(smem_u32(Vs), kFaKvHalf);
             auto issue_scores = [&](int t) {
-                const int st = t & 1;
-                if (!mbar_wait(smem_u32(&kv_full[st]), (t >> 1) & 1)) { ok = false; return; }
+                const int st = t % kFaStages;
+                if (!mbar_wait(smem_u32(&kv_full[st]), (t / kFaStages) & 1)) { ok = false; return; }
                 fa_fence_after();
-                const uint32_t qa = smem_u32(Qs), ka = smem_u32(Ks + st * TILE);
+                const uint64_t kd = k_desc + ((st * TILE) >> 4);
 #pragma unroll
-                for (int k16 = 0; k16 < HD / 16; ++k16) {
-                    const uint32_t o = (k16 >> 2) * kFaHalf + (k16 & 3) * 32;
-                    fa_umma(tmem_s + (t & 1) * kFaBN, fa_desc_kmajor(qa + o), fa_desc_kmajor(ka + o),
+                for (int k16 = 0; k16 < HD / 16; ++k16)
+                    fa_umma(tmem_s + (t & 1) * kFaBN,
+                            q_desc + (((k16 >> 2) * kFaHalf + (k16 & 3) * 32) >> 4),
+                            kd + (((k16 >> 2) * kFaKvHalf + (k16 & 3) * 32) >> 4),
                             idesc_qk, k16 > 0 ? 1u : 0u);
-                }
                 fa_commit(smem_u32(&s_full[t & 1]));
             };
+            // scores run two tiles ahead of the softmax: S(t + 2) is issued as soon as the
+            // softmax warps have read S(t), so they never wait for the tensor core
             if (ok) issue_scores(0);
+            if (ok && n_tiles > 1) issue_scores(1);
             for (int t = 0; t < n_tiles && ok; ++t) {
-                if (t + 1 < n_tiles) issue_scores(t + 1);      // overlaps this tile's softmax
-                if (!ok) break;
                 if (!mbar_wait(smem_u32(&p_full[t & 1]), (t >> 1) & 1)) { ok = false; break; }
                 fa_fence_after();
-                const int st = t & 1;
-                const uint32_t pa = smem_u32(Ps + (t & 1) * 2 * kFaHalf), va = smem_u32(Vs + st * TILE);
+                const int st = t % kFaStages;
+                const uint64_t pd = p_desc + (((t & 1) * kFaHalf) >> 4);
+                const uint64_t vd = v_desc + ((st * TILE) >> 4);
 #pragma unroll
-                for (int k16 = 0; k16 < kFaBN / 16; ++k16) {
-                    const uint32_t po = (k16 >> 2) * kFaHalf + (k16 & 3) * 32;
-                    fa_umma(tmem_pv, fa_desc_kmajor(pa + po),
-                            fa_desc_mnmajor(va + k16 * 16 * 128, kFaHalf), idesc_pv,
+                for (int k16 = 0; k16 < kFaBN / 16; ++k16)
+                    fa_umma(tmem_pv, pd + ((k16 * 32) >> 4), vd + ((k16 * 16 * 128) >> 4), idesc_pv,
                             (t > 0 || k16 > 0) ? 1u : 0u);     // O accumulates over the key tiles
-                }
                 fa_commit(smem_u32(&pv_full[t & 1]));
                 fa_commit(smem_u32(&kv_empty[st]));
+                if (t + 2 < n_tiles) issue_scores(t + 2);      // S buffer t & 1 has been read
             }
             if (!ok) {
                 failed_s = 1;
@@ -269,29 +284,30 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
     } else {
         // ---- softmax warps: a query row (one lane of tensor memory) is shared by two threads,
-        // one per half of the tile's 128 keys; they agree on the row maximum through shared memory
+        // one per half of the tile's 64 keys; they agree on the row maximum through shared memory
         const int q = warp & 3;                                  // lane quarter this warp may access
-        const int half = (warp - 2) >> 2;                        // which 64 keys of a tile
+        const int half = (warp - 2) >> 2;                        // which 32 keys of a tile
         const int row = q * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const int pos = q_pos0 + row;
         const int lo = window > 0 ? max(kv_first, pos - window + 1) : kv_first;
         float m = -INFINITY, l = 0.f;        // m: the reference maximum in use (log2 units)
         bool ok = true;
+        // The scores of a tile are fetched from tensor memory before the previous tile's
+        // probabilities are handed to the MMA warp: a load issued after that hand-over would
+        // queue behind the burst of MMAs it triggers.
+        uint32_t raw[32];
+        ok = mbar_wait(smem_u32(&s_full[0]), 0, 400000) && ok;
+        fa_fence_after();
+        fa_tmem_ld32_nowait(tmem_s + half * 32 + lane_addr, raw);
+        fa_tmem_wait_ld();
         for (int t = 0; t < n_tiles; ++t) {
-            const int kb = kb0 + t * kFaBN + half * 64;
-            ok = mbar_wait(smem_u32(&s_full[t & 1]), (t >> 1) & 1, ok ? 400000 : 1) && ok;
-            fa_fence_after();
-            const uint32_t s_addr = tmem_s + (t & 1) * kFaBN + half * 64 + lane_addr;
-            uint32_t raw[64];
-            fa_tmem_ld32_nowait(s_addr, raw);
-            fa_tmem_ld32_nowait(s_addr + 32, raw + 32);
-            fa_tmem_wait_ld();
-            float sv[64];
-            const bool inner = kb + 63 <= pos && kb >= lo;       // no hidden key for this row here
+            const int kb = kb0 + t * kFaBN + half * 32;
+            float sv[32];
+            const bool inner = kb + 31 <= pos && kb >= lo;       // no hidden key for this row here
             float tmax = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
+            for (int j = 0; j < 32; ++j) {
                 const int key = kb + j;
                 const float x = (inner || (key <= pos && key >= lo))
                                     ? __uint_as_float(raw[j]) * scale_log2e : -INFINITY;
@@ -332,9 +348,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             }
             const float neg_m = m == -INFINITY ? 0.f : -m;
             float psum = 0.f;
-            unsigned char* prow = Ps + (t & 1) * 2 * kFaHalf + half * kFaHalf + row * 128;
+            // 32 keys = 64 bytes = chunks 4 half .. 4 half + 3 of the row's 128-byte line
+            unsigned char* prow = Ps + (t & 1) * kFaHalf + row * 128;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
+            for (int ch = 0; ch < 4; ++ch) {
                 uint32_t pk[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -343,9 +360,16 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     psum += p0 + p1;
                     pk[j] = pack_bf16(p0, p1);
                 }
-                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                *reinterpret_cast<uint4*>(prow + (((half * 4 + ch) ^ (row & 7)) << 4)) =
+                    make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
             l += psum;
+            if (t + 1 < n_tiles) {
+                ok = mbar_wait(smem_u32(&s_full[(t + 1) & 1]), ((t + 1) >> 1) & 1, ok ? 400000 : 1) && ok;
+                fa_fence_after();
+                fa_tmem_ld32_nowait(tmem_s + ((t + 1) & 1) * kFaBN + half * 32 + lane_addr, raw);
+                fa_tmem_wait_ld();
+            }
             fa_fence_before();
             fence_proxy_async();                // P is read by the tensor core (async proxy)
             __syncwarp();
@@ -394,8 +418,7 @@ int launch_prefill_tc(const CUtensorMap* q_map, const CUtensorMap* kv_map, long 
                       long long v_row0, const int* block_table, int bt_stride, const int* cu_q,
                       const int* ctx_len, const int* tiles, int n_tiles, int nq, int nkv,
                       int page_size, float scale, int window, void* out, cudaStream_t stream) {
-    constexpr int TILE = (HD / 64) * kFaHalf;
-    const size_t smem = 5 * TILE + 4 * kFaHalf + 1024;
+    const size_t smem = (HD / 64) * kFaHalf + 2 * kFaStages * (HD / 64) * kFaKvHalf + 2 * kFaHalf + 1024;
     cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
     dim3 grid(n_tiles, nq);

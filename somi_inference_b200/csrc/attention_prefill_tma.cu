@@ -57,8 +57,11 @@ paged_prefill_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
         reinterpret_cast<uint4*>(Vs)[c] = make_uint4(0, 0, 0, 0);
     pdl_wait();
 
-    const int req = tiles[3 * blockIdx.x], row0 = tiles[3 * blockIdx.x + 1];
-    const int rows = tiles[3 * blockIdx.x + 2];
+    // later tiles of a prompt see more keys: they are started first so that the last CTAs
+    // to run are the short ones
+    const int tile = gridDim.x - 1 - blockIdx.x;
+    const int req = tiles[3 * tile], row0 = tiles[3 * tile + 1];
+    const int rows = tiles[3 * tile + 2];
     const int head = blockIdx.y, kvh = head / (nq / nkv);
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
     const int kv_end = q_pos0 + rows;
