@@ -175,12 +175,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const uint32_t tmem_s = tmem_base_s;                 // S buffers at columns 0 and 64
     const uint32_t tmem_pv = tmem_base_s + 128;
 
-    // later tiles of a prompt see more keys: they are started first so that the last CTAs
-    // to run are the short ones
-    const int tile = gridDim.x - 1 - blockIdx.x;
+    // later tiles of a prompt see more keys: blocks are handed out heads first, last tile
+    // first, so that the long ones of every head start early and the short ones fill the end
+    const int tile = gridDim.y - 1 - blockIdx.y;
     const int req = tiles[3 * tile], row0 = tiles[3 * tile + 1];
     const int rows = tiles[3 * tile + 2];
-    const int head = blockIdx.y, kvh = head / (nq / nkv);
+    const int head = blockIdx.x, kvh = head / (nq / nkv);
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
     const int kv_end = q_pos0 + rows;
     const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;
@@ -291,6 +291,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const int pos = q_pos0 + row;
         const int lo = window > 0 ? max(kv_first, pos - window + 1) : kv_first;
+        // the highest first visible key among the block's rows, and this row's visible span
+        const int lo_max = window > 0 ? max(kv_first, q_pos0 + kFaBM - 1 - window + 1) : kv_first;
+        const unsigned span = static_cast<unsigned>(pos - lo);
         float m = -INFINITY, l = 0.f;        // m: the reference maximum in use (log2 units)
         bool ok = true;
         // The scores of a tile are fetched from tensor memory before the previous tile's
@@ -304,19 +307,24 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         for (int t = 0; t < n_tiles; ++t) {
             const int kb = kb0 + t * kFaBN + half * 32;
             float sv[32];
-            const bool inner = kb + 31 <= pos && kb >= lo;       // no hidden key for this row here
+            // a tile in which no row of this block has a hidden key takes the short way
+            const bool tile_inner = kb0 + t * kFaBN + kFaBN - 1 <= q_pos0 && kb0 + t * kFaBN >= lo_max;
             float tmax = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const int key = kb + j;
-                const float x = (inner || (key <= pos && key >= lo))
-                                    ? __uint_as_float(raw[j]) * scale_log2e : -INFINITY;
+                float x = __uint_as_float(raw[j]);
+                if (!tile_inner) {
+                    // key in [lo, pos] as one unsigned comparison
+                    const unsigned d = static_cast<unsigned>(kb + j - lo);
+                    x = d <= span ? x : -INFINITY;
+                }
                 sv[j] = x;
                 tmax = fmaxf(tmax, x);
             }
             xmax_s[half][row] = tmax;
             fa_pair_sync(1 + q);
-            tmax = fmaxf(tmax, xmax_s[half ^ 1][row]);
+            // the scale is positive, so the maximum is taken over the raw scores and scaled once
+            tmax = fmaxf(tmax, xmax_s[half ^ 1][row]) * scale_log2e;
             // this tile's P buffer was last read by the product of tile t - 2
             if (t >= 2) ok = mbar_wait(smem_u32(&pv_full[t & 1]), ((t >> 1) - 1) & 1, ok ? 400000 : 1) && ok;
             // keep the old reference maximum unless the new one is more than 2^8 above it
@@ -355,8 +363,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 uint32_t pk[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const float p0 = fast_exp2(sv[ch * 8 + 2 * j] + neg_m);
-                    const float p1 = fast_exp2(sv[ch * 8 + 2 * j + 1] + neg_m);
+                    const float p0 = fast_exp2(fmaf(sv[ch * 8 + 2 * j], scale_log2e, neg_m));
+                    const float p1 = fast_exp2(fmaf(sv[ch * 8 + 2 * j + 1], scale_log2e, neg_m));
                     psum += p0 + p1;
                     pk[j] = pack_bf16(p0, p1);
                 }
@@ -421,7 +429,7 @@ int launch_prefill_tc(const CUtensorMap* q_map, const CUtensorMap* kv_map, long 
     const size_t smem = (HD / 64) * kFaHalf + 2 * kFaStages * (HD / 64) * kFaKvHalf + 2 * kFaHalf + 1024;
     cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
-    dim3 grid(n_tiles, nq);
+    dim3 grid(nq, n_tiles);
     launch_pdl(paged_prefill_tc_kernel<HD>, grid, dim3(kFaThreads), smem, stream, *q_map, *kv_map,
                k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len, tiles, nq, nkv, page_size,
                scale * 1.4426950408889634f, window, static_cast<__nv_bfloat16*>(out));
@@ -464,7 +472,7 @@ SOMI_API int somi_paged_attention_prefill_tc(
     int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, void* out,
     cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
-    if (!somi_prefill_tc_supported(nq, nkv, hd, page_size) || nq > 65535) return SOMI_ERR_UNSUPPORTED;
+    if (!somi_prefill_tc_supported(nq, nkv, hd, page_size) || n_tiles > 65535) return SOMI_ERR_UNSUPPORTED;
     const CUtensorMap* qm = static_cast<const CUtensorMap*>(q_map);
     const CUtensorMap* km = static_cast<const CUtensorMap*>(kv_map);
     if (hd == 64)
