@@ -23,8 +23,11 @@ namespace somi {
 
 constexpr int kFaBM = 128;               // query rows per CTA
 constexpr int kFaBN = 64;                // keys per tile
-constexpr int kFaStages = 4;             // key/value tiles in flight: a tile's copies take longer
-                                         // than a tile's arithmetic, so several must overlap
+// Key/value tiles in flight: a tile's copies take longer than a tile's arithmetic, so several
+// must overlap.  At head size 64 three stages leave room for two CTAs on an SM, whose softmax
+// and MMA phases then overlap each other.
+constexpr int kFaMaxStages = 4;
+__host__ __device__ constexpr int fa_stages(int hd) { return hd == 64 ? 3 : 4; }
 constexpr int kFaThreads = 320;          // producer warp, MMA warp, 8 softmax warps
 constexpr int kFaHalf = kFaBM * 128;     // bytes of one [128 rows][64 elements] swizzled block (Q, P)
 constexpr int kFaKvHalf = kFaBN * 128;   // bytes of one [64 keys][64 elements] block (K, V)
@@ -117,13 +120,14 @@ __device__ __forceinline__ void fa_fence_after() {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kFaThreads, 1)
+__global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1)
 paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                         const __grid_constant__ CUtensorMap kv_map, long long k_row0,
                         long long v_row0, const int* __restrict__ block_table, int bt_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                         const int* __restrict__ tiles, int nq, int nkv, int page_size,
-                        float scale_log2e, int window, __nv_bfloat16* __restrict__ out) {
+                        float scale_log2e, int window, __nv_bfloat16* __restrict__ out,
+                        int n_q_tiles, int first_wave) {
     constexpr int HALVES = HD / 64;
     constexpr int QTILE = HALVES * kFaHalf;              // bytes of the Q tile
     constexpr int TILE = HALVES * kFaKvHalf;             // bytes of a K or V tile
@@ -132,10 +136,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* Qs = base;
-    unsigned char* Ks = Qs + QTILE;                      // kFaStages tiles
-    unsigned char* Vs = Ks + kFaStages * TILE;           // kFaStages tiles
-    unsigned char* Ps = Vs + kFaStages * TILE;           // two buffers of 128 rows x 64 keys
-    __shared__ __align__(8) unsigned long long q_full, kv_full[kFaStages], kv_empty[kFaStages],
+    constexpr int STAGES = fa_stages(HD);
+    unsigned char* Ks = Qs + QTILE;                      // STAGES tiles
+    unsigned char* Vs = Ks + STAGES * TILE;           // STAGES tiles
+    unsigned char* Ps = Vs + STAGES * TILE;           // two buffers of 128 rows x 64 keys
+    __shared__ __align__(8) unsigned long long q_full, kv_full[kFaMaxStages], kv_empty[kFaMaxStages],
         s_full[2], p_full[2], pv_full[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
@@ -145,7 +150,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         mbar_init(smem_u32(&q_full), 1);
-        for (int s = 0; s < kFaStages; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(smem_u32(&kv_full[s]), 1);
             mbar_init(smem_u32(&kv_empty[s]), 1);
         }
@@ -165,7 +170,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     // value rows that no copy fills (pages outside the request's range) must be finite numbers
-    for (int c = tid; c < kFaStages * TILE / 16; c += kFaThreads)
+    for (int c = tid; c < STAGES * TILE / 16; c += kFaThreads)
         reinterpret_cast<uint4*>(Vs)[c] = make_uint4(0, 0, 0, 0);
     fence_proxy_async();
     fa_fence_before();
@@ -175,12 +180,17 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const uint32_t tmem_s = tmem_base_s;                 // S buffers at columns 0 and 64
     const uint32_t tmem_pv = tmem_base_s + 128;
 
-    // later tiles of a prompt see more keys: blocks are handed out heads first, last tile
-    // first, so that the long ones of every head start early and the short ones fill the end
-    const int tile = gridDim.y - 1 - blockIdx.y;
+    // Later tiles of a prompt see more keys.  Blocks are handed out longest first (heads
+    // first, last tile first), so that the short ones fill the end.  Where two blocks share an
+    // SM, the blocks of the second round, which start at once beside those of the first, are
+    // taken from the other end: the longest block then runs beside the shortest.
+    int rank = blockIdx.x;
+    if (first_wave > 0 && rank >= first_wave && rank < 2 * first_wave)
+        rank = min(2 * first_wave, static_cast<int>(gridDim.x)) - 1 - (rank - first_wave);
+    const int tile = n_q_tiles - 1 - rank / nq;
     const int req = tiles[3 * tile], row0 = tiles[3 * tile + 1];
     const int rows = tiles[3 * tile + 2];
-    const int head = blockIdx.x, kvh = head / (nq / nkv);
+    const int head = rank % nq, kvh = head / (nq / nkv);
     const int q_pos0 = ctx_len[req] + (row0 - cu_q[req]);
     const int kv_end = q_pos0 + rows;
     const int kv_first = window > 0 ? max(0, q_pos0 - window + 1) : 0;
@@ -200,7 +210,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
         const int pages_per_tile = kFaBN / page_size;
         for (int t = 0; t < n_tiles; ++t) {
-            const int st = t % kFaStages;
+            const int st = t % STAGES;
             const int kb = kb0 + t * kFaBN;
             const int p_lo = max(kb, kv_first) / page_size;
             const int p_hi = (min(kb + kFaBN, kv_end) - 1) / page_size;
@@ -211,7 +221,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             const uint32_t bar = smem_u32(&kv_full[st]);
             int ok = 1;
             if (lane == 0) {
-                ok = mbar_wait(smem_u32(&kv_empty[st]), ((t / kFaStages) & 1) ^ 1) ? 1 : 0;
+                ok = mbar_wait(smem_u32(&kv_empty[st]), ((t / STAGES) & 1) ^ 1) ? 1 : 0;
                 if (ok) mbar_expect_tx(bar, static_cast<uint32_t>(p_hi - p_lo + 1) * page_size * HD * 2 * 2);
                 else failed_s = 1;
             }
@@ -247,8 +257,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             const uint64_t p_desc = fa_desc_kmajor(smem_u32(Ps));
             const uint64_t v_desc = fa_desc_mnmajor(smem_u32(Vs), kFaKvHalf);
             auto issue_scores = [&](int t) {
-                const int st = t % kFaStages;
-                if (!mbar_wait(smem_u32(&kv_full[st]), (t / kFaStages) & 1)) { ok = false; return; }
+                const int st = t % STAGES;
+                if (!mbar_wait(smem_u32(&kv_full[st]), (t / STAGES) & 1)) { ok = false; return; }
                 fa_fence_after();
                 const uint64_t kd = k_desc + ((st * TILE) >> 4);
 #pragma unroll
@@ -266,7 +276,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             for (int t = 0; t < n_tiles && ok; ++t) {
                 if (!mbar_wait(smem_u32(&p_full[t & 1]), (t >> 1) & 1)) { ok = false; break; }
                 fa_fence_after();
-                const int st = t % kFaStages;
+                const int st = t % STAGES;
                 const uint64_t pd = p_desc + (((t & 1) * kFaHalf) >> 4);
                 const uint64_t vd = v_desc + ((st * TILE) >> 4);
 #pragma unroll
@@ -325,8 +335,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             fa_pair_sync(1 + q);
             // the scale is positive, so the maximum is taken over the raw scores and scaled once
             tmax = fmaxf(tmax, xmax_s[half ^ 1][row]) * scale_log2e;
-            // this tile's P buffer was last read by the product of tile t - 2
-            if (t >= 2) ok = mbar_wait(smem_u32(&pv_full[t & 1]), ((t >> 1) - 1) & 1, ok ? 400000 : 1) && ok;
+            // This tile's P buffer was last read by the product of tile t - 2.  That product was
+            // issued before the scores of tile t, and a commit covers everything issued before
+            // it, so the wait for S(t) has covered it already.
             // keep the old reference maximum unless the new one is more than 2^8 above it
             float alpha = 1.f;
             bool rescale = false;
@@ -426,13 +437,21 @@ int launch_prefill_tc(const CUtensorMap* q_map, const CUtensorMap* kv_map, long 
                       long long v_row0, const int* block_table, int bt_stride, const int* cu_q,
                       const int* ctx_len, const int* tiles, int n_tiles, int nq, int nkv,
                       int page_size, float scale, int window, void* out, cudaStream_t stream) {
-    const size_t smem = (HD / 64) * kFaHalf + 2 * kFaStages * (HD / 64) * kFaKvHalf + 2 * kFaHalf + 1024;
+    const size_t smem = (HD / 64) * kFaHalf + 2 * fa_stages(HD) * (HD / 64) * kFaKvHalf + 2 * kFaHalf + 1024;
     cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
-    dim3 grid(nq, n_tiles);
+    static int sm_count = 0;
+    if (sm_count == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    }
+    const int first_wave = HD == 64 ? sm_count : 0;      // two blocks per SM at head size 64
+    dim3 grid(static_cast<unsigned>(nq) * n_tiles);
     launch_pdl(paged_prefill_tc_kernel<HD>, grid, dim3(kFaThreads), smem, stream, *q_map, *kv_map,
                k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len, tiles, nq, nkv, page_size,
-               scale * 1.4426950408889634f, window, static_cast<__nv_bfloat16*>(out));
+               scale * 1.4426950408889634f, window, static_cast<__nv_bfloat16*>(out), n_tiles,
+               first_wave);
     return launch_status();
 }
 
@@ -472,7 +491,7 @@ SOMI_API int somi_paged_attention_prefill_tc(
     int n_tiles, int nq, int nkv, int hd, int page_size, float scale, int window, void* out,
     cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
-    if (!somi_prefill_tc_supported(nq, nkv, hd, page_size) || n_tiles > 65535) return SOMI_ERR_UNSUPPORTED;
+    if (!somi_prefill_tc_supported(nq, nkv, hd, page_size) ) return SOMI_ERR_UNSUPPORTED;
     const CUtensorMap* qm = static_cast<const CUtensorMap*>(q_map);
     const CUtensorMap* km = static_cast<const CUtensorMap*>(kv_map);
     if (hd == 64)

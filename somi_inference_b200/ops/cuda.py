@@ -65,7 +65,6 @@ class CudaOps:
         self.prefill_tc_q_tile = int(self.lib.somi_prefill_tc_q_tile())
         self.q_tile_sizes = (self.generic_q_tile, self.prefill_q_tile, self.prefill_tc_q_tile)
         self.use_tc_prefill = True
-        self.force_tc_prefill = False      # tests: take the tcgen05 kernel wherever it is supported
         self._q_maps: dict = {}
         self.lib.somi_decode_chunk.restype = ctypes.c_int
         self.decode_chunk = int(self.lib.somi_decode_chunk())
@@ -251,9 +250,9 @@ class CudaOps:
             tma = (self.use_tma_prefill and storage is not None and bool(
                 self.lib.somi_prefill_tma_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
                                                     ctypes.c_int(hd), ctypes.c_int(page_size))))
-            # measured on 2,048-token prompts: the tcgen05 kernel is ahead at head size 128
-            # (146 vs 160 us per 7B-shaped layer) and behind at 64 (90 vs 68 us)
-            tc = (self.use_tc_prefill and (hd == 128 or self.force_tc_prefill)
+            # measured on 2,048-token prompts: the tcgen05 kernel is ahead at both of its head
+            # sizes (74 vs 160 us per 7B-shaped layer, 44 vs 67 us per 0.5B-shaped layer)
+            tc = (self.use_tc_prefill
                   and storage is not None and qkv.shape[1] % 8 == 0 and bool(
                 self.lib.somi_prefill_tc_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
                                                    ctypes.c_int(hd), ctypes.c_int(page_size))))

@@ -237,7 +237,7 @@ def test_tensor_core_prefill_attention(ops, case, path):
                                               window=window, requests=reqs, dtype=torch.bfloat16,
                                               seed=11)
     out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
-    ops.use_tc_prefill = ops.force_tc_prefill = path == "tcgen05"
+    ops.use_tc_prefill = path == "tcgen05"
     ops.use_tma_prefill = path != "cp_async"
     try:
         ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
@@ -245,7 +245,6 @@ def test_tensor_core_prefill_attention(ops, case, path):
         ops.check_errors()
     finally:
         ops.use_tma_prefill = ops.use_tc_prefill = True
-        ops.force_tc_prefill = False
     ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
     cb = batch_to_cpu(batch)
     HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), cb, cb.groups[0], nq, nkv,
