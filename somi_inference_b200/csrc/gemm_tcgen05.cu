@@ -159,7 +159,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                 for (int k16 = 0; k16 < kGemmBK / 16; ++k16)
                     umma_bf16(tmem_d, umma_smem_desc(wa + k16 * 32), umma_smem_desc(xa + k16 * 32),
                               idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
-                umma_commit(smem_u32(&empty_bar[s]));          // the stage is free once these MMAs have read it
+                // the stage is free once these MMAs have read it; nobody waits for a stage that
+                // is not filled again
+                if (kb + STAGES < nkb) umma_commit(smem_u32(&empty_bar[s]));
             }
             umma_commit(smem_u32(&accum_bar));                 // accumulator complete
         }
@@ -209,7 +211,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                     if ((lane & 1) == 0 && n < N && m < M) {
                         const float g = acc[m];
                         y[static_cast<size_t>(m) * half_n + (n >> 1)] =
-                            __float2bfloat16_rn(g / (1.0f + expf(-g)) * other);
+                            __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * other);
                     }
                 }
             }
