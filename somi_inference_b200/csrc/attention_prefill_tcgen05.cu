@@ -24,10 +24,11 @@ namespace somi {
 constexpr int kFaBM = 128;               // query rows per CTA
 constexpr int kFaBN = 64;                // keys per tile
 // Key/value tiles in flight: a tile's copies take longer than a tile's arithmetic, so several
-// must overlap.  At head size 64 three stages leave room for two CTAs on an SM, whose softmax
-// and MMA phases then overlap each other.
+// must overlap.  One CTA per SM: two of them on an SM (tried at head size 64, where registers
+// and shared memory allow it) were no faster than one, the softmax of a tile being bound by
+// the SM's throughput, not by latency that a second CTA could hide.
 constexpr int kFaMaxStages = 4;
-__host__ __device__ constexpr int fa_stages(int hd) { return hd == 64 ? 3 : 4; }
+__host__ __device__ constexpr int fa_stages(int) { return 4; }
 constexpr int kFaThreads = 320;          // producer warp, MMA warp, 8 softmax warps
 constexpr int kFaHalf = kFaBM * 128;     // bytes of one [128 rows][64 elements] swizzled block (Q, P)
 constexpr int kFaKvHalf = kFaBN * 128;   // bytes of one [64 keys][64 elements] block (K, V)
@@ -120,14 +121,14 @@ __device__ __forceinline__ void fa_fence_after() {
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kFaThreads, HD == 64 ? 2 : 1)
+__global__ void __launch_bounds__(kFaThreads, 1)
 paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                         const __grid_constant__ CUtensorMap kv_map, long long k_row0,
                         long long v_row0, const int* __restrict__ block_table, int bt_stride,
                         const int* __restrict__ cu_q, const int* __restrict__ ctx_len,
                         const int* __restrict__ tiles, int nq, int nkv, int page_size,
                         float scale_log2e, int window, __nv_bfloat16* __restrict__ out,
-                        int n_q_tiles, int first_wave) {
+                        int n_q_tiles) {
     constexpr int HALVES = HD / 64;
     constexpr int QTILE = HALVES * kFaHalf;              // bytes of the Q tile
     constexpr int TILE = HALVES * kFaKvHalf;             // bytes of a K or V tile
@@ -181,12 +182,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const uint32_t tmem_pv = tmem_base_s + 128;
 
     // Later tiles of a prompt see more keys.  Blocks are handed out longest first (heads
-    // first, last tile first), so that the short ones fill the end.  Where two blocks share an
-    // SM, the blocks of the second round, which start at once beside those of the first, are
-    // taken from the other end: the longest block then runs beside the shortest.
-    int rank = blockIdx.x;
-    if (first_wave > 0 && rank >= first_wave && rank < 2 * first_wave)
-        rank = min(2 * first_wave, static_cast<int>(gridDim.x)) - 1 - (rank - first_wave);
+    // first, last tile first), so that the short ones fill the end.
+    const int rank = blockIdx.x;
     const int tile = n_q_tiles - 1 - rank / nq;
     const int req = tiles[3 * tile], row0 = tiles[3 * tile + 1];
     const int rows = tiles[3 * tile + 2];
@@ -440,18 +437,10 @@ int launch_prefill_tc(const CUtensorMap* q_map, const CUtensorMap* kv_map, long 
     const size_t smem = (HD / 64) * kFaHalf + 2 * fa_stages(HD) * (HD / 64) * kFaKvHalf + 2 * kFaHalf + 1024;
     cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-    }
-    const int first_wave = HD == 64 ? sm_count : 0;      // two blocks per SM at head size 64
     dim3 grid(static_cast<unsigned>(nq) * n_tiles);
     launch_pdl(paged_prefill_tc_kernel<HD>, grid, dim3(kFaThreads), smem, stream, *q_map, *kv_map,
                k_row0, v_row0, block_table, bt_stride, cu_q, ctx_len, tiles, nq, nkv, page_size,
-               scale * 1.4426950408889634f, window, static_cast<__nv_bfloat16*>(out), n_tiles,
-               first_wave);
+               scale * 1.4426950408889634f, window, static_cast<__nv_bfloat16*>(out), n_tiles);
     return launch_status();
 }
 

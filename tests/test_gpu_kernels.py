@@ -223,6 +223,9 @@ PREFILL_CASES = [
     (2, 2, 128, 64, None, [(3, 61), (0, 64), (0, 65)]),
     (7, 1, 64, 16, None, [(0, 700), (1500, 100)]),
     (4, 2, 128, 8, 70, [(0, 400), (333, 90)]),
+    # more than 16 key tiles: the tcgen05 kernel runs such a block as two halves and adds them
+    (4, 2, 128, 8, 1200, [(900, 400), (2000, 130)]),
+    (3, 1, 64, 16, None, [(0, 1300), (1100, 50)]),
 ]
 
 
