@@ -68,7 +68,9 @@ class StepBatch:
     tiles: dict[int, torch.Tensor]  # q-tile size -> int32 [n_tiles, 3] (request, first row, rows)
     groups: list[GroupBatch]
     host: HostBatch
-    layout_key: tuple = field(default_factory=tuple)   # sizes that fix every offset in the buffer
+    # the sizes that fix every offset in the buffer, then the multi-token requests and their tokens:
+    # two steps with equal keys launch the same kernels with the same arguments
+    layout_key: tuple = field(default_factory=tuple)
 
 
 _NO_TILES = np.zeros((0, 3), dtype=np.int64)
@@ -220,7 +222,7 @@ class BatchBuilder:
             state_slot=dv(5), logit_rows=dv(6), tiles=tiles, groups=groups,
             host=HostBatch(cu_q=cu_q, ctx_len=ctx, state_slot=slots,
                            requests=[entries[i].request for i in order]),
-            layout_key=tuple(sizes),
+            layout_key=tuple(sizes) + (n_prefill, n_prefill_tokens),
         )
         return batch, order
 
@@ -298,7 +300,7 @@ class BatchBuilder:
             logit_rows=fixed[6], tiles=tiles, groups=groups,
             host=HostBatch(cu_q=np.arange(R + 1, dtype=np.int64), ctx_len=pos_np,
                            state_slot=slots_np, requests=reqs),
-            layout_key=tuple(sizes))
+            layout_key=tuple(sizes) + (0, 0))
         return batch, list(range(R))
 
     def _upload(self, sizes, arrays) -> tuple[list[int], int]:

@@ -92,6 +92,7 @@ class Engine:
         self.last_batch: StepBatch | None = None
         self.use_graphs = use_graphs
         self.max_graphs = 64
+        self.graph_max_tokens = 8192     # larger steps are bound by the GPU, not by the host
         self._graphs: dict[tuple, tuple] = {}
         self._seen: dict[tuple, int] = {}
         self._graph_pool = None
@@ -138,13 +139,15 @@ class Engine:
         return self._run(batch, keep)
 
     def _run(self, batch: StepBatch, keep: bool = True) -> torch.Tensor:
-        """Forward pass of one batch.  Steps that hold only single-token requests are launch
-        bound, so their kernel sequence is captured in a CUDA graph the second time a layout
-        (batch size, table width, wanted rows) is seen and replayed from then on; the batch
-        descriptor lives at fixed device addresses, so a replay reads the new step's data."""
+        """Forward pass of one batch.  A step is a sequence of a few hundred kernels; for
+        single-token steps and for portions of a small model the host cannot issue them as fast
+        as the GPU runs them.  So the kernel sequence is captured in a CUDA graph the second time
+        a layout (tokens and rows of every request class, tiles, table width, wanted rows) is
+        seen and replayed from then on; the batch descriptor lives at fixed device addresses, so
+        a replay reads the new step's data."""
         self.last_batch = batch
-        graphable = (self.use_graphs and batch.num_prefill_requests == 0
-                     and self.device.type == "cuda" and self.model.graph_safe)
+        graphable = (self.use_graphs and self.device.type == "cuda" and self.model.graph_safe
+                     and batch.num_tokens <= self.graph_max_tokens)
         if not graphable:
             with torch.no_grad():
                 return self.model.forward(batch, self.cache)
@@ -163,6 +166,8 @@ class Engine:
             return logits.clone() if keep else logits
         with torch.no_grad():
             logits = self.model.forward(batch, self.cache)      # also warms up the libraries
+        if len(self._seen) > 4096:       # many layouts that never came back
+            self._seen.clear()
         self._seen[key] = self._seen.get(key, 0) + 1
         if self._seen[key] >= 2 and len(self._graphs) < self.max_graphs:
             # Capturing runs nothing; recording the same step again is harmless because a step
