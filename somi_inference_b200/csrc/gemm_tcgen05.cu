@@ -8,6 +8,10 @@
 // Warp roles: warp 0 = TMA producer (one thread issues `cp.async.bulk.tensor` loads of W and X
 // tiles, 128-byte swizzle, into a ring of shared-memory stages), warp 1 = MMA issuer (one thread
 // issues `tcgen05.mma`, `tcgen05.commit` hands stages back and finally signals the accumulator),
+// warp 6 = a second MMA issuer: the two take the K blocks in turn, each into an accumulator of
+// its own (the thread that issues MMAs has no queue in front of the tensor pipe, so the pipe
+// idles for the ~220 cycles that thread spends on each barrier test; with two threads one
+// thread's test runs under the other's MMAs), the epilogue adds the two accumulators;
 // warps 2-5 = epilogue (`tcgen05.ld` of their 32 lanes, then bias / SiLU(gate)*up / float32
 // output and coalesced stores).  All waits on mbarriers are bounded; a wait that runs out sets
 // an error word, and the CTA still frees its tensor memory and returns.
@@ -21,7 +25,7 @@ namespace somi {
 
 constexpr int kGemmBN = 128;              // output features per CTA (MMA M)
 constexpr int kGemmBK = 64;               // K per stage: 64 bf16 = one 128-byte swizzle row
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 224;
 constexpr int kGemmWBytes = kGemmBN * kGemmBK * 2;      // 16 KiB
 
 enum GemmMode { kGemmBf16 = 0, kGemmF32 = 1, kGemmPartialF32 = 2, kGemmSwiGLU = 3 };
@@ -76,7 +80,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                    void* __restrict__ out, long long out_split_stride) {
     constexpr int XBytes = TOK * kGemmBK * 2;
     constexpr int StageBytes = kGemmWBytes + XBytes;
-    constexpr int TmemCols = TOK < 32 ? 32 : TOK;
+    constexpr int TmemCols = 2 * TOK < 32 ? 32 : 2 * TOK;     // one accumulator per MMA thread
     extern __shared__ unsigned char smem_raw[];
     unsigned char* stages = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -97,7 +101,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
             mbar_init(smem_u32(&full_bar[s]), 1);
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
-        mbar_init(smem_u32(&accum_bar), 1);
+        mbar_init(smem_u32(&accum_bar), 2);         // one arrival per MMA thread
         mbar_fence_init();
         failed_s = 0;
     }
@@ -141,14 +145,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                 tma_load_2d(smem_u32(st + kGemmWBytes), &x_map, (kb0 + kb) * kGemmBK, 0, fb);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 6) {
         if (lane == 0) {
+            const int par = warp == 1 ? 0 : 1;       // this thread's K blocks: par, par + 2, ...
+            const uint32_t tmem_acc = tmem_d + par * TOK;
             // instruction descriptor: float32 accumulator, bf16 x bf16, both K-major, N = TOK, M = 128
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
                                    (static_cast<uint32_t>(TOK >> 3) << 17) |
                                    (static_cast<uint32_t>(kGemmBN >> 4) << 24);
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; ++kb) {
+            for (int kb = par; kb < nkb && ok; kb += 2) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
                 if (!mbar_wait(smem_u32(&full_bar[s]), ph)) { failed_s = 1; ok = false; break; }
@@ -157,8 +163,8 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                 const uint32_t xa = wa + kGemmWBytes;
 #pragma unroll
                 for (int k16 = 0; k16 < kGemmBK / 16; ++k16)
-                    umma_bf16(tmem_d, umma_smem_desc(wa + k16 * 32), umma_smem_desc(xa + k16 * 32),
-                              idesc, (kb > 0 || k16 > 0) ? 1u : 0u);
+                    umma_bf16(tmem_acc, umma_smem_desc(wa + k16 * 32), umma_smem_desc(xa + k16 * 32),
+                              idesc, (kb > par || k16 > 0) ? 1u : 0u);
                 // the stage is free once these MMAs have read it; nobody waits for a stage that
                 // is not filled again
                 if (kb + STAGES < nkb) umma_commit(smem_u32(&empty_bar[s]));
@@ -182,6 +188,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                 for (int j = 0; j < 16; ++j) acc[c * 16 + j] = __uint_as_float(r[j]);
             }
             asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+            if (nkb > 1) {          // the second thread's accumulator holds the odd K blocks
+#pragma unroll
+                for (int c = 0; c < TOK / 16; ++c) {
+                    uint32_t r[16];
+                    tmem_load_16(tmem_d + (static_cast<uint32_t>(q * 32) << 16) + TOK + c * 16, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[c * 16 + j] += __uint_as_float(r[j]);
+                }
+            }
         } else {
 #pragma unroll
             for (int j = 0; j < TOK; ++j) acc[j] = 0.f;
