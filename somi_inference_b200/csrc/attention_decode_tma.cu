@@ -65,13 +65,19 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ float m_s[kTdWarps][kTdRows], l_s[kTdWarps][kTdRows];
     pdl_launch_dependents();
-    pdl_wait();
+    // The kernel before this one wrote the step's own keys and values (one position per request
+    // here) and the queries.  Lengths, block tables and every older cache page were complete
+    // before that kernel started, so their copies are issued before the dependency wait and
+    // fly while it finishes; only the page of the newest position and Q come after the wait.
 
     const int split = blockIdx.x, kvh = blockIdx.y, i = blockIdx.z;
     const int req = req_base + i, row = row_base + i;
     const int G = nq / nkv;
     const TdRange rg = td_range(ctx_len[req], window);
-    if (split < rg.first_split || split >= rg.n_splits) return;
+    if (split < rg.first_split || split >= rg.n_splits) {
+        pdl_wait();
+        return;
+    }
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int k0 = split * kTdChunk;
     const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
@@ -82,6 +88,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     const int first_page = max(k0, rg.first_key) / page_size;             // absolute index
     const int last_page = (min(k0 + kTdChunk, rg.kv_len) - 1) / page_size;
     const int chunk_page0 = k0 / page_size;
+    const int newest_page = (rg.kv_len - 1) / page_size;                  // written by the predecessor
 
     // Warp 0 starts the copies before anything else: lane 0 arms both barriers with the byte
     // counts, then one lane per page looks its page up and issues that page's copies, so the
@@ -98,7 +105,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
         __syncwarp();
         for (int p = lane; p < pages_in_chunk; p += 32) {
             const int ap = chunk_page0 + p;
-            if (ap < first_page || ap > last_page) continue;
+            if (ap < first_page || ap > last_page || ap == newest_page) continue;
             const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
             const int r = p * page_size;
 #pragma unroll
@@ -119,6 +126,21 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
             const int r = p * page_size + c / CPR, ch = c % CPR;
             *reinterpret_cast<uint4*>(Vs + tma_tile_offset(r, ch)) = make_uint4(0, 0, 0, 0);
         }
+    }
+    pdl_wait();
+    if (warp == 0 && newest_page >= max(first_page, chunk_page0) &&
+        newest_page <= last_page && lane == (newest_page - chunk_page0) % 32) {
+        const int p = newest_page - chunk_page0;
+        const long long prow = (static_cast<long long>(bt[newest_page]) * nkv + kvh) * page_size;
+        const int r = p * page_size;
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h)
+            tma_load_2d(smem_u32(Ks + h * kHalfBytes + r * 128), &kv_map, h * 64,
+                        static_cast<int>(k_row0 + prow), bar_k);
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h)
+            tma_load_2d(smem_u32(Vs + h * kHalfBytes + r * 128), &kv_map, h * 64,
+                        static_cast<int>(v_row0 + prow), bar_v);
     }
     // Q: rows of the group's heads, zero rows up to 16
     const __nv_bfloat16* qrow = qkv + static_cast<size_t>(row) * row_stride + static_cast<size_t>(kvh) * G * HD;

@@ -146,12 +146,17 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ residual, const T
     __shared__ float slice_ss;
     cg::cluster_group cluster = cg::this_cluster();
     pdl_launch_dependents();
-    pdl_wait();
     const int csize = static_cast<int>(cluster.num_blocks());
     const int rank = static_cast<int>(cluster.block_rank());
     const int b = blockIdx.x / csize;
-    const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
     const int c0 = rank * cols_per_cta, c1 = min(H, c0 + cols_per_cta);
+    // the norm's weight is a constant of the model: fetched while the kernel before this one
+    // finishes (a thread's first four columns; a slice seldom has more per thread)
+    const int i_first = c0 + threadIdx.x * 4;
+    F4 w_first = F4{{0.f, 0.f, 0.f, 0.f}};
+    if (i_first < c1) w_first = load4_any(weight, weight_dtype, i_first);
+    pdl_wait();
+    const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
     float* r = residual + row * H;
     const TD* d = delta ? delta + row * H : nullptr;
     float ss = 0.f;
@@ -180,7 +185,7 @@ __global__ void add_rmsnorm_cluster_kernel(float* __restrict__ residual, const T
     TO* o = out + static_cast<size_t>(b) * H;
     for (int i = c0 + threadIdx.x * 4; i < c1; i += blockDim.x * 4) {
         F4 v = load4(row_buf + (i - c0));
-        const F4 w = load4_any(weight, weight_dtype, i);
+        const F4 w = i == i_first ? w_first : load4_any(weight, weight_dtype, i);
 #pragma unroll
         for (int k = 0; k < 4; ++k) v.v[k] = v.v[k] * inv * w.v[k];
         store4(o + i, v);
@@ -199,7 +204,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   T* __restrict__ kcache, T* __restrict__ vcache, int page_size) {
     extern __shared__ float cs[];   // cos[rot/2], sin[rot/2]
     pdl_launch_dependents();
-    pdl_wait();
+    // positions, frequencies and slots belong to the step's descriptor, not to the kernel before
+    // this one: the angles are ready when the projection is
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const float pos = static_cast<float>(positions[t]);
@@ -209,9 +215,10 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
         cs[i] = c;
         cs[half + i] = s;
     }
+    const int slot = slot_map ? slot_map[t] : -1;
+    pdl_wait();
     __syncthreads();
     T* row = qkv + static_cast<size_t>(t) * (nq + 2 * nkv) * hd;
-    const int slot = slot_map ? slot_map[t] : -1;
     const int page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? slot % page_size : 0;
     // queries and keys: rotated pairs (two neighbouring pairs per thread where sizes allow)
@@ -287,7 +294,6 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
                                           int heads_per_cta) {
     extern __shared__ float cs[];
     pdl_launch_dependents();
-    pdl_wait();
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int width = (nq + 2 * nkv) * hd;
@@ -298,6 +304,8 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
         cs[i] = c;
         cs[half + i] = s;
     }
+    const int slot = slot_map ? slot_map[t] : -1;
+    pdl_wait();             // the partial sums are the only input the kernel before this one wrote
     __syncthreads();
     const float* prow = parts + static_cast<size_t>(t) * width;
     auto value = [&](int col) {
@@ -316,7 +324,6 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
         return v;
     };
     __nv_bfloat16* qrow = q_out + static_cast<size_t>(t) * width;
-    const int slot = slot_map ? slot_map[t] : -1;
     const int page = slot >= 0 ? slot / page_size : 0;
     const int off = slot >= 0 ? slot % page_size : 0;
     // this CTA's share of the nq + 2 nkv heads (queries, keys, values in that order)
