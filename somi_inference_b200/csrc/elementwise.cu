@@ -82,6 +82,10 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
     pdl_launch_dependents();
+    // the norm's weight is a constant of the model: a thread's first four columns are fetched
+    // while the kernel before this one finishes
+    F4 w_first = F4{{0.f, 0.f, 0.f, 0.f}};
+    if ((H & 3) == 0 && threadIdx.x * 4 < H) w_first = load4_any(weight, weight_dtype, threadIdx.x * 4);
     pdl_wait();
     const int b = blockIdx.x;
     const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
@@ -109,7 +113,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
         const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
             F4 v = load4(row_buf + i);
-            const F4 w = load4_any(weight, weight_dtype, i);
+            const F4 w = i == threadIdx.x * 4 ? w_first : load4_any(weight, weight_dtype, i);
 #pragma unroll
             for (int k = 0; k < 4; ++k) v.v[k] = v.v[k] * inv * w.v[k];
             store4(o + i, v);
@@ -277,6 +281,99 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
         const int head = idx / hd, i = idx - head * hd;
         vcache[((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i] = v[idx];
+    }
+}
+
+// The bfloat16 case for many tokens (prompt portions): four tokens per CTA, 16-byte accesses.
+// A work item is 8 consecutive dims of one head: a rotated pair of 8-dim groups (i, i + rot/2)
+// of a query or key head, 8 unrotated key dims, or 8 value dims.  Needs rot/2, hd - rot and hd
+// to be multiples of 8 and 16-byte aligned rows.
+constexpr int kRopeToks = 4;
+__device__ __forceinline__ void unpack8(const uint4& r, float (&f)[8]) {
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        f[2 * k] = __uint_as_float(w[k] << 16);
+        f[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * k], f[2 * k + 1]);
+        w[k] = *reinterpret_cast<const uint32_t*>(&p);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__global__ void __launch_bounds__(256)
+rope_store_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                         const float* __restrict__ inv_freq, int T, int nq, int nkv, int hd, int rot,
+                         const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ kcache,
+                         __nv_bfloat16* __restrict__ vcache, int page_size) {
+    extern __shared__ float cs[];                 // per token: cos[rot/2], sin[rot/2]
+    __shared__ int slot_s[kRopeToks];
+    pdl_launch_dependents();
+    const int t0 = blockIdx.x * kRopeToks;
+    const int n_tok = min(kRopeToks, T - t0);
+    const int half = rot >> 1;
+    for (int idx = threadIdx.x; idx < n_tok * half; idx += blockDim.x) {
+        const int tt = idx / half, i = idx - tt * half;
+        float sn, c;
+        sincosf(static_cast<float>(positions[t0 + tt]) * inv_freq[i], &sn, &c);
+        cs[tt * rot + i] = c;
+        cs[tt * rot + half + i] = sn;
+    }
+    if (threadIdx.x < n_tok) slot_s[threadIdx.x] = slot_map ? slot_map[t0 + threadIdx.x] : -1;
+    pdl_wait();
+    __syncthreads();
+    const int width = (nq + 2 * nkv) * hd;
+    const int g_rot = half >> 3, g_tail = (hd - rot) >> 3, g_v = hd >> 3;
+    const int n_rot = (nq + nkv) * g_rot;               // rotated pairs of the q and k heads
+    const int n_qtail = 0;                              // unrotated query dims stay where they are
+    const int n_ktail = nkv * g_tail, n_val = nkv * g_v;
+    const int per_tok = n_rot + n_qtail + n_ktail + n_val;
+    for (int idx = threadIdx.x; idx < n_tok * per_tok; idx += blockDim.x) {
+        const int tt = idx / per_tok;
+        int w = idx - tt * per_tok;
+        __nv_bfloat16* row = qkv + static_cast<size_t>(t0 + tt) * width;
+        const int slot = slot_s[tt];
+        const int page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+        if (w < n_rot) {
+            const int head = w / g_rot, i = (w - head * g_rot) << 3;
+            __nv_bfloat16* x = row + static_cast<size_t>(head) * hd;
+            float a[8], b[8], o1[8], o2[8];
+            unpack8(*reinterpret_cast<const uint4*>(x + i), a);
+            unpack8(*reinterpret_cast<const uint4*>(x + i + half), b);
+            const float* c = cs + tt * rot + i;
+            const float* sn = c + half;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                o1[k] = a[k] * c[k] - b[k] * sn[k];
+                o2[k] = b[k] * c[k] + a[k] * sn[k];
+            }
+            const uint4 r1 = pack8(o1), r2 = pack8(o2);
+            *reinterpret_cast<uint4*>(x + i) = r1;
+            *reinterpret_cast<uint4*>(x + i + half) = r2;
+            if (slot >= 0 && head >= nq) {
+                __nv_bfloat16* kc = kcache + ((static_cast<size_t>(page) * nkv + (head - nq)) * page_size + off) * hd;
+                *reinterpret_cast<uint4*>(kc + i) = r1;
+                *reinterpret_cast<uint4*>(kc + i + half) = r2;
+            }
+            continue;
+        }
+        if (slot < 0) continue;
+        w -= n_rot;
+        if (w < n_ktail) {
+            const int head = w / g_tail, i = rot + ((w - head * g_tail) << 3);
+            *reinterpret_cast<uint4*>(kcache + ((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i) =
+                *reinterpret_cast<const uint4*>(row + static_cast<size_t>(nq + head) * hd + i);
+            continue;
+        }
+        w -= n_ktail;
+        const int head = w / g_v, i = (w - head * g_v) << 3;
+        *reinterpret_cast<uint4*>(vcache + ((static_cast<size_t>(page) * nkv + head) * page_size + off) * hd + i) =
+            *reinterpret_cast<const uint4*>(row + static_cast<size_t>(nq + nkv + head) * hd + i);
     }
 }
 
@@ -554,6 +651,15 @@ SOMI_API int somi_rope_store(void* qkv, int dtype, const int* positions, const f
     if (T <= 0) return 0;
     if (rot < 0 || rot > hd || (rot & 1)) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>(rot > 0 ? rot : 2) * sizeof(float);
+    const auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (dtype == SOMI_BF16 && T > 32 && rot > 0 && (rot & 15) == 0 && ((hd - rot) & 7) == 0 &&
+        (hd & 7) == 0 && aligned16(qkv) && aligned16(kcache) && aligned16(vcache)) {
+        launch_pdl(rope_store_bf16x8_kernel, dim3((T + kRopeToks - 1) / kRopeToks), dim3(256),
+                   smem * kRopeToks, stream, static_cast<__nv_bfloat16*>(qkv), positions, inv_freq, T,
+                   nq, nkv, hd, rot, slot_map, static_cast<__nv_bfloat16*>(kcache),
+                   static_cast<__nv_bfloat16*>(vcache), page_size);
+        return launch_status();
+    }
     if (dtype == SOMI_F32)
         launch_pdl(rope_store_kernel<float>, dim3(T), dim3(256), smem, stream, 
             static_cast<float*>(qkv), positions, inv_freq, nq, nkv, hd, rot, slot_map,
