@@ -39,7 +39,9 @@ def test_embed(ops, dtype, V, H, T):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("wdtype", DTYPES)
-@pytest.mark.parametrize("N,H", [(9, 80), (4, 896), (3, 3584), (2, 5120), (5, 8192)])
+@pytest.mark.parametrize("N,H", [(9, 80), (4, 896), (3, 3584), (2, 5120), (5, 8192),
+                                 # more than 32 rows: a warp per row up to 2,048 columns
+                                 (70, 896), (45, 1540), (33, 80), (100, 2048), (41, 2052)])
 def test_add_rmsnorm(ops, dtype, wdtype, N, H):
     g = torch.Generator().manual_seed(2)
     res = torch.randn(N, H, generator=g) * 3
@@ -255,9 +257,10 @@ def test_tensor_core_prefill_attention(ops, case, path):
     torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(torch.bfloat16))
 
 
-def test_add_rmsnorm_sums_partial_deltas(ops):
+@pytest.mark.parametrize("N", [7, 50])
+def test_add_rmsnorm_sums_partial_deltas(ops, N):
     g = torch.Generator().manual_seed(5)
-    N, H, S = 7, 896, 5
+    H, S = 896, 5
     res = torch.randn(N, H, generator=g)
     parts = torch.randn(S, N, H, generator=g)
     w = (1 + 0.1 * torch.randn(H, generator=g)).to(torch.bfloat16)
