@@ -69,6 +69,7 @@ class CudaOps:
         self.lib.somi_decode_chunk.restype = ctypes.c_int
         self.decode_chunk = int(self.lib.somi_decode_chunk())
         self._workspace = None
+        self._device_index = torch.cuda.current_device()
         self._tensor_maps: dict = {}
         self.use_tma_decode = True
         self.use_tma_prefill = True
@@ -83,9 +84,10 @@ class CudaOps:
             self.use_skinny_gemm = False
 
     # ------------------------------------------------------------------ util
-    @staticmethod
-    def _stream() -> ctypes.c_void_p:
-        return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    def _stream(self) -> ctypes.c_void_p:
+        # the raw handle of the current stream, without the Python stream object in between:
+        # that path costs microseconds per launch, which a step of hundreds of launches feels
+        return ctypes.c_void_p(torch._C._cuda_getCurrentRawStream(self._device_index))
 
     def _done(self, rc: int, what: str) -> None:
         self.launches += 1

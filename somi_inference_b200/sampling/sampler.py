@@ -77,13 +77,15 @@ class Sampler:
             buf[h:h + n_hist] = np.concatenate(toks)
         self.h2d_bytes_last = buf.nbytes
         dev = torch.from_numpy(buf).to(self.device, non_blocking=True)
-        return dev, r8, o, h, n_hist
+        # the kernel's arguments as views of the one uploaded buffer (made once per upload: the
+        # block of an all-greedy step is cached with them)
+        return (dev[0:rows].view(torch.float32), dev[r8:r8 + rows],
+                dev[2 * r8:2 * r8 + rows].view(torch.float32),
+                dev[3 * r8:3 * r8 + rows].view(torch.float32),
+                dev[4 * r8:4 * r8 + 2 * rows], dev[6 * r8:6 * r8 + rows],
+                dev[o:o + rows + 1], dev[h:h + max(n_hist, 1)])
 
-    def _launch(self, logits, rows, dev, r8, o, h, n_hist):
+    def _launch(self, logits, rows, *views):
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
-        self.ops.sample(logits, dev[0:rows].view(torch.float32), dev[r8:r8 + rows],
-                        dev[2 * r8:2 * r8 + rows].view(torch.float32),
-                        dev[3 * r8:3 * r8 + rows].view(torch.float32),
-                        dev[4 * r8:4 * r8 + 2 * rows], dev[6 * r8:6 * r8 + rows],
-                        dev[o:o + rows + 1], dev[h:h + max(n_hist, 1)], out)
+        self.ops.sample(logits, *views, out)
         return out
