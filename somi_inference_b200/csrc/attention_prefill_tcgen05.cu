@@ -1,18 +1,24 @@
 // Prompt-portion attention over the paged cache on the 5th-generation tensor cores.
 //
-// One CTA = up to 128 consecutive query rows of one request x one query head; key tiles of 64
-// positions aligned to multiples of 64, four of them in flight.  Both products run as
-// `tcgen05.mma` with accumulators in tensor memory: S = Q K^T (128 x 64, two buffers so that the
-// next tile's scores are computed while this tile's softmax runs) and O += P V (128 x head_dim).  Operands come from
-// shared memory in the 128-byte-swizzle layout: Q and the K/V pages by `cp.async.bulk.tensor.2d`
-// (V is the MN-major operand of the second product, so the cache's [key][dim] rows are used as
-// they are), P written by the softmax warps.  Warp roles: warp 0 producer (TMA), warp 1 MMA
+// One CTA = up to 128 consecutive query rows of one request x one query head; key tiles of 128
+// positions aligned to multiples of 128.  Both products run as `tcgen05.mma` with accumulators
+// in tensor memory: S = Q K^T (128 x 128, two buffers, issued two tiles ahead of the softmax)
+// and O += P V (128 x head_dim).  Operands come from shared memory in the 128-byte-swizzle
+// layout: Q and the K/V pages by `cp.async.bulk.tensor.2d` (V is the MN-major operand of the
+// second product, so the cache's [key][dim] rows are used as they are), P written by the
+// softmax warps.  Keys and values have rings of their own: a key tile is free again as soon as
+// its scores are computed, a value tile only after the second product, so the keys can be
+// fetched two tiles ahead with two stages.  Warp roles: warp 0 producer (TMA), warp 1 MMA
 // issuer, warps 2-9 softmax: a query row is one lane of tensor memory and is served by two
-// threads (one per 64 of a tile's 128 keys) that agree on the row maximum through shared memory.  The output accumulates in tensor
-// memory across key tiles; it is rescaled there (tcgen05.ld / tcgen05.st) only when a row's
-// maximum grows by more than 2^8, otherwise the old maximum keeps serving as the reference
-// (probabilities up to 256 are harmless in float32 sums and bfloat16 operands), so most tiles
-// cost the softmax warps one pass over S and one over P.  Softmax is float32, base 2.  Every wait on an mbarrier is bounded and failure is recorded in an error word.
+// threads (one per 64 of a tile's 128 keys) that agree on the row maximum through shared
+// memory.  The output accumulates in tensor memory across key tiles; it is rescaled there
+// (tcgen05.ld / tcgen05.st) only when a row's maximum grows by more than 2^8, otherwise the old
+// maximum keeps serving as the reference (probabilities up to 256 are harmless in float32 sums
+// and bfloat16 operands), so most tiles cost the softmax warps one pass over S and one over P.
+// A tile's fixed costs (barrier tests, tensor-memory load latency, the exchange of maxima, the
+// proxy fence) are paid once per 128 keys: with 64-key tiles the same kernel took 1.5 times as
+// long.  Softmax is float32, base 2.  Every wait on an mbarrier is bounded and failure is
+// recorded in an error word.
 //
 // The reference's prefill kernel (somi_inference/core/flash_attention_triton.py:31-194) is a
 // FlashAttention-2 loop on `tl.dot`; formulas in somi_inference/models/qwen2.py:158-186.
@@ -22,16 +28,13 @@
 namespace somi {
 
 constexpr int kFaBM = 128;               // query rows per CTA
-constexpr int kFaBN = 64;                // keys per tile
-// Key/value tiles in flight: a tile's copies take longer than a tile's arithmetic, so several
-// must overlap.  One CTA per SM: two of them on an SM (tried at head size 64, where registers
-// and shared memory allow it) were no faster than one, the softmax of a tile being bound by
-// the SM's throughput, not by latency that a second CTA could hide.
+constexpr int kFaBN = 128;               // keys per tile
+// Key and value tiles in flight, as many as shared memory holds beside Q and the two P buffers.
 constexpr int kFaMaxStages = 4;
-__host__ __device__ constexpr int fa_stages(int) { return 4; }
-constexpr int kFaThreads = 320;          // producer warp, MMA warp, 8 softmax warps
+__host__ __device__ constexpr int fa_stages(int hd) { return hd == 128 ? 2 : 4; }
+constexpr int kFaThreads = 352;          // K producer warp, MMA warp, 8 softmax warps, V producer warp
 constexpr int kFaHalf = kFaBM * 128;     // bytes of one [128 rows][64 elements] swizzled block (Q, P)
-constexpr int kFaKvHalf = kFaBN * 128;   // bytes of one [64 keys][64 elements] block (K, V)
+constexpr int kFaKvHalf = kFaBN * 128;   // bytes of one [128 keys][64 elements] block (K, V)
 
 __device__ int g_prefill_tc_error = 0;
 
@@ -132,7 +135,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     constexpr int HALVES = HD / 64;
     constexpr int QTILE = HALVES * kFaHalf;              // bytes of the Q tile
     constexpr int TILE = HALVES * kFaKvHalf;             // bytes of a K or V tile
-    constexpr uint32_t TmemCols = 256;                   // S0 | S1 (64 each) | PV (up to 128)
+    constexpr uint32_t TmemCols = 512;                   // S0 | S1 (128 each) | PV (up to 128)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -140,9 +143,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     constexpr int STAGES = fa_stages(HD);
     unsigned char* Ks = Qs + QTILE;                      // STAGES tiles
     unsigned char* Vs = Ks + STAGES * TILE;           // STAGES tiles
-    unsigned char* Ps = Vs + STAGES * TILE;           // two buffers of 128 rows x 64 keys
-    __shared__ __align__(8) unsigned long long q_full, kv_full[kFaMaxStages], kv_empty[kFaMaxStages],
-        s_full[2], p_full[2], pv_full[2];
+    unsigned char* Ps = Vs + STAGES * TILE;           // two buffers of two [128 rows][64 keys] blocks
+    __shared__ __align__(8) unsigned long long q_full, k_full[kFaMaxStages], k_empty[kFaMaxStages],
+        v_full[kFaMaxStages], v_empty[kFaMaxStages], s_full[2], p_full[2], pv_full[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
     __shared__ float xmax_s[2][kFaBM];       // exchanged between the two warps that share a row
@@ -152,8 +155,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     if (tid == 0) {
         mbar_init(smem_u32(&q_full), 1);
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&kv_full[s]), 1);
-            mbar_init(smem_u32(&kv_empty[s]), 1);
+            mbar_init(smem_u32(&k_full[s]), 1);
+            mbar_init(smem_u32(&k_empty[s]), 1);
+            mbar_init(smem_u32(&v_full[s]), 1);
+            mbar_init(smem_u32(&v_empty[s]), 1);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);
@@ -178,8 +183,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     __syncthreads();
     fa_fence_after();
     pdl_wait();
-    const uint32_t tmem_s = tmem_base_s;                 // S buffers at columns 0 and 64
-    const uint32_t tmem_pv = tmem_base_s + 128;
+    const uint32_t tmem_s = tmem_base_s;                 // S buffers at columns 0 and 128
+    const uint32_t tmem_pv = tmem_base_s + 2 * kFaBN;
 
     // Later tiles of a prompt see more keys.  Blocks are handed out longest first (heads
     // first, last tile first), so that the short ones fill the end.
@@ -195,10 +200,12 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const int n_tiles = (kv_end - kb0 + kFaBN - 1) / kFaBN;
     const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
 
-    if (warp == 0) {
-        // producer warp: lane 0 keeps the barriers, one lane per page looks its page up and
-        // issues that page's copies, so the page-table reads of a tile run side by side
-        if (lane == 0) {
+    if (warp == 0 || warp == 10) {
+        // producer warps, one for the keys (and Q) and one for the values: a copy of a 16-token
+        // page is a small box, and what bounds a warp is the number of copies it issues.
+        // Lane 0 keeps the barriers, one lane per page looks its page up and issues that
+        // page's copies, so the page-table reads of a tile run side by side.
+        if (warp == 0 && lane == 0) {
             mbar_expect_tx(smem_u32(&q_full), kFaBM * HD * 2);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
@@ -206,7 +213,8 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                             smem_u32(&q_full));
         }
         const int pages_per_tile = kFaBN / page_size;
-        for (int t = 0; t < n_tiles; ++t) {
+        // one tile's keys (which = 0) or values (which = 1) into stage t % STAGES of their ring
+        auto load_tile = [&](int t, int which) -> bool {
             const int st = t % STAGES;
             const int kb = kb0 + t * kFaBN;
             const int p_lo = max(kb, kv_first) / page_size;
@@ -215,27 +223,29 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             int my_page = -1;
             const int ap = kb / page_size + lane;
             if (lane < pages_per_tile && ap >= p_lo && ap <= p_hi) my_page = bt[ap];
-            const uint32_t bar = smem_u32(&kv_full[st]);
+            const uint32_t bar = smem_u32(which ? &v_full[st] : &k_full[st]);
             int ok = 1;
             if (lane == 0) {
-                ok = mbar_wait(smem_u32(&kv_empty[st]), ((t / STAGES) & 1) ^ 1) ? 1 : 0;
-                if (ok) mbar_expect_tx(bar, static_cast<uint32_t>(p_hi - p_lo + 1) * page_size * HD * 2 * 2);
+                ok = mbar_wait(smem_u32(which ? &v_empty[st] : &k_empty[st]), ((t / STAGES) & 1) ^ 1) ? 1 : 0;
+                if (ok) mbar_expect_tx(bar, static_cast<uint32_t>(p_hi - p_lo + 1) * page_size * HD * 2);
                 else failed_s = 1;
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (!ok) break;
+            if (!ok) return false;
             if (my_page >= 0) {
                 const long long prow = (static_cast<long long>(my_page) * nkv + kvh) * page_size;
                 const int r = lane * page_size;
+                unsigned char* dst = (which ? Vs : Ks) + st * TILE + r * 128;
 #pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    tma_load_2d(smem_u32(Ks + st * TILE + h * kFaKvHalf + r * 128), &kv_map, h * 64,
-                                static_cast<int>(k_row0 + prow), bar);
-                    tma_load_2d(smem_u32(Vs + st * TILE + h * kFaKvHalf + r * 128), &kv_map, h * 64,
-                                static_cast<int>(v_row0 + prow), bar);
-                }
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_2d(smem_u32(dst + h * kFaKvHalf), &kv_map, h * 64,
+                                static_cast<int>((which ? v_row0 : k_row0) + prow), bar);
             }
-        }
+            return true;
+        };
+        const int which = warp == 0 ? 0 : 1;
+        for (int t = 0; t < n_tiles; ++t)
+            if (!load_tile(t, which)) break;
     } else if (warp == 1) {
         if (lane == 0) {
             // float32 accumulators, bf16 operands; scores: both K-major, N = 128 keys;
@@ -255,7 +265,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             const uint64_t v_desc = fa_desc_mnmajor(smem_u32(Vs), kFaKvHalf);
             auto issue_scores = [&](int t) {
                 const int st = t % STAGES;
-                if (!mbar_wait(smem_u32(&kv_full[st]), (t / STAGES) & 1)) { ok = false; return; }
+                if (!mbar_wait(smem_u32(&k_full[st]), (t / STAGES) & 1)) { ok = false; return; }
                 fa_fence_after();
                 const uint64_t kd = k_desc + ((st * TILE) >> 4);
 #pragma unroll
@@ -265,23 +275,26 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                             kd + (((k16 >> 2) * kFaKvHalf + (k16 & 3) * 32) >> 4),
                             idesc_qk, k16 > 0 ? 1u : 0u);
                 fa_commit(smem_u32(&s_full[t & 1]));
+                fa_commit(smem_u32(&k_empty[st]));             // the key tile is free once these ran
             };
             // scores run two tiles ahead of the softmax: S(t + 2) is issued as soon as the
             // softmax warps have read S(t), so they never wait for the tensor core
             if (ok) issue_scores(0);
             if (ok && n_tiles > 1) issue_scores(1);
             for (int t = 0; t < n_tiles && ok; ++t) {
+                const int st = t % STAGES;
+                if (!mbar_wait(smem_u32(&v_full[st]), (t / STAGES) & 1)) { ok = false; break; }
                 if (!mbar_wait(smem_u32(&p_full[t & 1]), (t >> 1) & 1)) { ok = false; break; }
                 fa_fence_after();
-                const int st = t % STAGES;
-                const uint64_t pd = p_desc + (((t & 1) * kFaHalf) >> 4);
+                const uint64_t pd = p_desc + (((t & 1) * 2 * kFaHalf) >> 4);
                 const uint64_t vd = v_desc + ((st * TILE) >> 4);
 #pragma unroll
                 for (int k16 = 0; k16 < kFaBN / 16; ++k16)
-                    fa_umma(tmem_pv, pd + ((k16 * 32) >> 4), vd + ((k16 * 16 * 128) >> 4), idesc_pv,
+                    fa_umma(tmem_pv, pd + (((k16 >> 2) * kFaHalf + (k16 & 3) * 32) >> 4),
+                            vd + ((k16 * 16 * 128) >> 4), idesc_pv,
                             (t > 0 || k16 > 0) ? 1u : 0u);     // O accumulates over the key tiles
                 fa_commit(smem_u32(&pv_full[t & 1]));
-                fa_commit(smem_u32(&kv_empty[st]));
+                fa_commit(smem_u32(&v_empty[st]));
                 if (t + 2 < n_tiles) issue_scores(t + 2);      // S buffer t & 1 has been read
             }
             if (!ok) {
@@ -289,11 +302,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 // let the softmax warps run out of their bounded waits instead of hanging
             }
         }
-    } else {
+    } else if (warp < 10) {
         // ---- softmax warps: a query row (one lane of tensor memory) is shared by two threads,
-        // one per half of the tile's 64 keys; they agree on the row maximum through shared memory
+        // one per half of the tile's 128 keys; they agree on the row maximum through shared memory
         const int q = warp & 3;                                  // lane quarter this warp may access
-        const int half = (warp - 2) >> 2;                        // which 32 keys of a tile
+        const int half = (warp - 2) >> 2;                        // which 64 keys of a tile
         const int row = q * 32 + lane;
         const uint32_t lane_addr = static_cast<uint32_t>(q * 32) << 16;
         const int pos = q_pos0 + row;
@@ -303,31 +316,31 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         const unsigned span = static_cast<unsigned>(pos - lo);
         float m = -INFINITY, l = 0.f;        // m: the reference maximum in use (log2 units)
         bool ok = true;
-        // The scores of a tile are fetched from tensor memory before the previous tile's
-        // probabilities are handed to the MMA warp: a load issued after that hand-over would
-        // queue behind the burst of MMAs it triggers.
-        uint32_t raw[32];
-        ok = mbar_wait(smem_u32(&s_full[0]), 0, 400000) && ok;
-        fa_fence_after();
-        fa_tmem_ld32_nowait(tmem_s + half * 32 + lane_addr, raw);
-        fa_tmem_wait_ld();
         for (int t = 0; t < n_tiles; ++t) {
-            const int kb = kb0 + t * kFaBN + half * 32;
-            float sv[32];
+            ok = mbar_wait(smem_u32(&s_full[t & 1]), (t >> 1) & 1, ok ? 400000 : 1) && ok;
+            fa_fence_after();
+            uint32_t ra[32], rb[32];
+            const uint32_t s_addr = tmem_s + (t & 1) * kFaBN + half * 64 + lane_addr;
+            fa_tmem_ld32_nowait(s_addr, ra);
+            fa_tmem_ld32_nowait(s_addr + 32, rb);
+            fa_tmem_wait_ld();
+            const int kb = kb0 + t * kFaBN + half * 64;
+            float sv[64];
             // a tile in which no row of this block has a hidden key takes the short way
             const bool tile_inner = kb0 + t * kFaBN + kFaBN - 1 <= q_pos0 && kb0 + t * kFaBN >= lo_max;
-            float tmax = -INFINITY;
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};      // four chains, not one
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                float x = __uint_as_float(raw[j]);
+            for (int j = 0; j < 64; ++j) {
+                float x = __uint_as_float(j < 32 ? ra[j] : rb[j - 32]);
                 if (!tile_inner) {
                     // key in [lo, pos] as one unsigned comparison
                     const unsigned d = static_cast<unsigned>(kb + j - lo);
                     x = d <= span ? x : -INFINITY;
                 }
                 sv[j] = x;
-                tmax = fmaxf(tmax, x);
+                mx[j & 3] = fmaxf(mx[j & 3], x);
             }
+            float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
             xmax_s[half][row] = tmax;
             fa_pair_sync(1 + q);
             // the scale is positive, so the maximum is taken over the raw scores and scaled once
@@ -363,29 +376,24 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 l *= alpha;
             }
             const float neg_m = m == -INFINITY ? 0.f : -m;
-            float psum = 0.f;
-            // 32 keys = 64 bytes = chunks 4 half .. 4 half + 3 of the row's 128-byte line
-            unsigned char* prow = Ps + (t & 1) * kFaHalf + row * 128;
+            float ps[2] = {0.f, 0.f};
+            // this thread's 64 keys are one 128-byte line of its [128 rows][64 keys] block
+            unsigned char* prow = Ps + (t & 1) * 2 * kFaHalf + half * kFaHalf + row * 128;
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
+            for (int ch = 0; ch < 8; ++ch) {
                 uint32_t pk[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float p0 = fast_exp2(fmaf(sv[ch * 8 + 2 * j], scale_log2e, neg_m));
                     const float p1 = fast_exp2(fmaf(sv[ch * 8 + 2 * j + 1], scale_log2e, neg_m));
-                    psum += p0 + p1;
+                    ps[0] += p0;
+                    ps[1] += p1;
                     pk[j] = pack_bf16(p0, p1);
                 }
-                *reinterpret_cast<uint4*>(prow + (((half * 4 + ch) ^ (row & 7)) << 4)) =
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (row & 7)) << 4)) =
                     make_uint4(pk[0], pk[1], pk[2], pk[3]);
             }
-            l += psum;
-            if (t + 1 < n_tiles) {
-                ok = mbar_wait(smem_u32(&s_full[(t + 1) & 1]), ((t + 1) >> 1) & 1, ok ? 400000 : 1) && ok;
-                fa_fence_after();
-                fa_tmem_ld32_nowait(tmem_s + ((t + 1) & 1) * kFaBN + half * 32 + lane_addr, raw);
-                fa_tmem_wait_ld();
-            }
+            l += ps[0] + ps[1];
             fa_fence_before();
             fence_proxy_async();                // P is read by the tensor core (async proxy)
             __syncwarp();
@@ -434,7 +442,7 @@ int launch_prefill_tc(const CUtensorMap* q_map, const CUtensorMap* kv_map, long 
                       long long v_row0, const int* block_table, int bt_stride, const int* cu_q,
                       const int* ctx_len, const int* tiles, int n_tiles, int nq, int nkv,
                       int page_size, float scale, int window, void* out, cudaStream_t stream) {
-    const size_t smem = (HD / 64) * kFaHalf + 2 * fa_stages(HD) * (HD / 64) * kFaKvHalf + 2 * kFaHalf + 1024;
+    const size_t smem = (HD / 64) * kFaHalf + 2 * fa_stages(HD) * (HD / 64) * kFaKvHalf + 4 * kFaHalf + 1024;
     cudaFuncSetAttribute(paged_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
     dim3 grid(static_cast<unsigned>(nq) * n_tiles);
