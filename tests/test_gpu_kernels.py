@@ -177,6 +177,49 @@ def test_attention_far_key_and_window_edge(ops, dtype, window):
         assert close == seen, f"key at {spot}: seen={seen}, output equals its value: {close}"
 
 
+@pytest.mark.parametrize("window", [None, 130])
+@pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 128), (6, 2, 64)])
+def test_prefill_attention_far_key_and_window_edge(ops, nq, nkv, hd, window):
+    """The same for a prompt portion (the tcgen05 kernel): one key is made to dominate for one
+    query row; that row's output must be the key's value, or must not see it.  Rows at the first
+    and last position of the portion and on both sides of a 128-row tile edge; keys far back, on
+    both sides of the 128-key tile edges, in the first and last slot of a page, on the diagonal,
+    one beyond the diagonal (hidden), on the window's edge (seen) and one beyond it (hidden)."""
+    ps, ctx, qn = 16, 300, 200
+    mgr, batch, qkv, view, _ = attention_case(ops, nq=nq, nkv=nkv, hd=hd, page_size=ps,
+                                              window=window, requests=[(ctx, qn)],
+                                              dtype=torch.bfloat16, seed=3)
+    table = batch.groups[0].block_table[0].cpu()
+    q = qkv.view(qn, nq + 2 * nkv, hd)
+    G = nq // nkv
+    for r in (0, 127, 128, qn - 1):
+        qpos = ctx + r
+        if window is None:
+            spots = [5, 127, 128, 255, 256, 16 * 20, 16 * 21 - 1, qpos, qpos + 1]
+        else:
+            spots = [qpos - window + 1, qpos - window, qpos]
+        for spot in spots:
+            if spot >= ctx + qn:
+                continue
+            keys = view.keys.clone()
+            page, off = int(table[spot // ps]), spot % ps
+            for h in range(nkv):
+                keys[page, h, off] = (q[r, h * G].float() * 20).to(torch.bfloat16)
+            out = torch.empty(qn, nq * hd, dtype=torch.bfloat16, device="cuda")
+            store = view.storage.clone()
+            ks, vs = store[0, 0], store[0, 1]
+            ks.copy_(keys)
+            ops.paged_attention(qkv, ks, vs, batch, batch.groups[0], nq, nkv, hd, hd ** -0.5,
+                                window, out, storage=store)
+            ops.check_errors()
+            got = out.view(qn, nq, hd)[r, 0].float()
+            planted = view.values[page, 0, off].float()
+            seen = spot <= qpos and (window is None or spot > qpos - window)
+            close = torch.allclose(got, planted, rtol=2e-2, atol=2e-2)
+            assert close == seen, (f"row {r} (position {qpos}), key at {spot}: seen={seen}, "
+                                   f"output equals its value: {close}")
+
+
 DECODE_CASES = [
     # nq nkv hd ps window ctx lengths (each request brings one token)
     (14, 2, 64, 16, None, [0, 1, 126, 127, 128, 129, 255, 256, 1000, 2047]),
