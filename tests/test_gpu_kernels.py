@@ -228,6 +228,9 @@ DECODE_CASES = [
     (3, 3, 32, 64, None, [130, 64, 63]),
     (14, 2, 64, 16, 200, [10, 199, 200, 201, 500, 383, 384, 385]),
     (8, 4, 128, 32, 128, [127, 128, 129, 1000]),
+    # long contexts: many chunks per request
+    (14, 2, 64, 16, None, [3900, 100, 2300]),
+    (4, 2, 128, 16, None, [5000, 3]),
 ]
 
 
@@ -268,7 +271,7 @@ PREFILL_CASES = [
     (2, 2, 128, 64, None, [(3, 61), (0, 64), (0, 65)]),
     (7, 1, 64, 16, None, [(0, 700), (1500, 100)]),
     (4, 2, 128, 8, 70, [(0, 400), (333, 90)]),
-    # more than 16 key tiles: the tcgen05 kernel runs such a block as two halves and adds them
+    # long key ranges (more than 1,024 keys for a block of queries)
     (4, 2, 128, 8, 1200, [(900, 400), (2000, 130)]),
     (3, 1, 64, 16, None, [(0, 1300), (1100, 50)]),
 ]
