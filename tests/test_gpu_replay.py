@@ -21,6 +21,8 @@ pytestmark = pytest.mark.gpu
 # units and a wrong key or a wrong mask moves the logits by far more than the tolerance.
 STD = 0.08
 LENGTHS = [5, 97, 40, 70, 33, 100, 64, 81]
+# D: several 128-key tiles and 128-row query tiles, and lengths on both sides of their edges
+LENGTHS_BY_MODEL = {"D": [300, 150, 260, 33, 129, 200]}
 # float32: logits are of size 3-5; differences between orders of summation stay below 3e-5.
 # bfloat16: every activation that passes between kernels is rounded to 8 bits of mantissa
 # (2^-9 relative each).  Measured on whole prompts (no cache or batching involved) and under
@@ -45,7 +47,7 @@ def models(tmp_path_factory):
             d = make_model(name, root, dt, std=STD)
             cfg, w = plain.load_folder(d)       # float32 arithmetic on the stored values
             reqs = {f"r{i}": random_tokens(n, cfg["vocab_size"], 10 + i)
-                    for i, n in enumerate(LENGTHS)}
+                    for i, n in enumerate(LENGTHS_BY_MODEL.get(name, LENGTHS))}
             ref = {k: plain.logits(cfg, w, v) for k, v in reqs.items()}
             scale = max(v.abs().max().item() for v in ref.values())
             out[(name, dt)] = (d, cfg, reqs, ref, scale)
@@ -67,7 +69,7 @@ def test_replay_in_process(models, name, dtype, mode):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["B", "C"])
+@pytest.mark.parametrize("name", ["B", "C", "D"])
 def test_replay_program(models, tmp_path, name, dtype):
     d, cfg, reqs, ref, scale = models[(name, getattr(torch, dtype))]
     for mode in ("mixed", "last32"):

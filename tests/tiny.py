@@ -4,7 +4,8 @@ A and B are the two tiny shapes of the benchmark description (they differ in
 every size: layers, width, heads, groups, head size, intermediate size,
 vocabulary, theta, eps, tied or untied head).  C adds what neither has: a
 sliding window on the upper layers, an explicit head_dim that is not
-hidden/heads, and sizes that are no power of two.
+hidden/heads, and sizes that are no power of two.  D has head size 128 and is
+run with sequences of a few hundred tokens.
 """
 
 from __future__ import annotations
@@ -29,9 +30,16 @@ TINY_C = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden
               intermediate_size=176, vocab_size=517, rope_theta=50000.0, rms_norm_eps=3e-6,
               tie_word_embeddings=False, max_position_embeddings=320, use_sliding_window=True,
               sliding_window=24, max_window_layers=1, hidden_act="silu")
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 2}
-PAGE_SIZES = {"A": 16, "B": 8, "C": 16}
+# D has the head size of the large models (128) and room for sequences of several key tiles and
+# several 128-row query tiles; its upper layer has a window that is longer than a key tile.
+TINY_D = dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", num_hidden_layers=2,
+              hidden_size=256, num_attention_heads=2, num_key_value_heads=1, head_dim=128,
+              intermediate_size=384, vocab_size=700, rope_theta=1000000.0, rms_norm_eps=1e-6,
+              tie_word_embeddings=True, max_position_embeddings=512, use_sliding_window=True,
+              sliding_window=160, max_window_layers=1, hidden_act="silu")
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+PAGE_SIZES = {"A": 16, "B": 8, "C": 16, "D": 16}
 
 
 def make_model(name: str, root: str, dtype=torch.float32, std: float = 0.02) -> str:
