@@ -70,9 +70,12 @@ inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 // Every kernel of this library is launched with the programmatic-serialization attribute: it
 // may be scheduled while its predecessor in the stream is still running, so that its launch
 // latency and its set-up (barriers, tensor memory, index arithmetic) overlap the predecessor's
-// tail.  The rule that makes this safe: a kernel calls `pdl_wait()` before its first access to
-// global memory that another kernel writes or reads, and before any early return; it calls
-// `pdl_launch_dependents()` as its first statement so that its own successor may be scheduled.
+// tail.  The rule that makes this safe: a kernel calls `pdl_wait()` before it writes global
+// memory at all, before it reads anything its predecessor writes, and before any early return;
+// it calls `pdl_launch_dependents()` as its first statement so that its own successor may be
+// scheduled.  What only earlier kernels or the host wrote (weights, the step's descriptor, cache
+// pages of older positions) may be read before the wait: every kernel finishes only after its
+// own wait, so everything before the predecessor is complete when the predecessor runs.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -81,27 +84,6 @@ __device__ __forceinline__ void pdl_launch_dependents() {
 inline int& pdl_enabled() {
     static int on = 1;
     return on;
-}
-
-// The same with a thread-block cluster of `cluster_x` CTAs along x (grid.x must be a multiple).
-template <typename... KArgs, typename... Args>
-inline int launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                              cudaStream_t stream, unsigned cluster_x, Args&&... args) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = block;
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[2];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster_x;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    return static_cast<int>(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
 }
 
 template <typename... KArgs, typename... Args>

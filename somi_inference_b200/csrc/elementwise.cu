@@ -1,7 +1,6 @@
 // Memory-bound kernels of a decoder step: embedding gather, residual sum fused
 // with RMS normalisation, rotary encoding fused with the cache write, SiLU(gate)*up.
 // All arithmetic is float32; inputs and outputs are float32 or bfloat16.
-#include <cooperative_groups.h>
 
 #include "common.cuh"
 
@@ -132,68 +131,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
     for (int i = threadIdx.x; i < H; i += blockDim.x)
         o[i] = from_float<TO>(row_buf[i] * inv * load_as_float(weight, weight_dtype, i));
-}
-
-// The same for few rows: a cluster of CTAs shares one row, each CTA owning a slice of the
-// columns, and the slices' sums of squares meet through distributed shared memory.  With one CTA
-// per row a step of 8 tokens would keep 8 SMs busy; this keeps 8 * cluster size.
-template <typename TD, typename TO>
-__global__ void add_rmsnorm_cluster_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
-                                           int splits, long long split_stride,
-                                           const void* __restrict__ weight, int weight_dtype,
-                                           float eps, TO* __restrict__ out,
-                                           const int* __restrict__ rows, int H, int write_back,
-                                           int cols_per_cta) {
-    namespace cg = cooperative_groups;
-    extern __shared__ __align__(16) float row_buf[];          // this CTA's slice of the row
-    __shared__ float scratch[33];
-    __shared__ float slice_ss;
-    cg::cluster_group cluster = cg::this_cluster();
-    pdl_launch_dependents();
-    const int csize = static_cast<int>(cluster.num_blocks());
-    const int rank = static_cast<int>(cluster.block_rank());
-    const int b = blockIdx.x / csize;
-    const int c0 = rank * cols_per_cta, c1 = min(H, c0 + cols_per_cta);
-    // the norm's weight is a constant of the model: fetched while the kernel before this one
-    // finishes (a thread's first four columns; a slice seldom has more per thread)
-    const int i_first = c0 + threadIdx.x * 4;
-    F4 w_first = F4{{0.f, 0.f, 0.f, 0.f}};
-    if (i_first < c1) w_first = load4_any(weight, weight_dtype, i_first);
-    pdl_wait();
-    const size_t row = rows ? static_cast<size_t>(rows[b]) : static_cast<size_t>(b);
-    float* r = residual + row * H;
-    const TD* d = delta ? delta + row * H : nullptr;
-    float ss = 0.f;
-    for (int i = c0 + threadIdx.x * 4; i < c1; i += blockDim.x * 4) {
-        F4 v = load4(r + i);
-        if (d) {
-#pragma unroll 4
-            for (int sp = 0; sp < splits; ++sp) {
-                const F4 dv = load4(d + sp * split_stride + i);
-#pragma unroll
-                for (int k = 0; k < 4; ++k) v.v[k] += dv.v[k];
-            }
-            if (write_back) store4(r + i, v);
-        }
-        store4(row_buf + (i - c0), v);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) ss += v.v[k] * v.v[k];
-    }
-    ss = block_sum(ss, scratch);
-    if (threadIdx.x == 0) slice_ss = ss;
-    cluster.sync();
-    float total = 0.f;
-    for (int k = 0; k < csize; ++k) total += *cluster.map_shared_rank(&slice_ss, k);
-    cluster.sync();            // nobody leaves while its neighbours still read its sum
-    const float inv = 1.0f / sqrtf(total / static_cast<float>(H) + eps);
-    TO* o = out + static_cast<size_t>(b) * H;
-    for (int i = c0 + threadIdx.x * 4; i < c1; i += blockDim.x * 4) {
-        F4 v = load4(row_buf + (i - c0));
-        const F4 w = i == i_first ? w_first : load4_any(weight, weight_dtype, i);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) v.v[k] = v.v[k] * inv * w.v[k];
-        store4(o + i, v);
-    }
 }
 
 // ------------------------------------------- rotary encoding + cache write
@@ -604,29 +541,12 @@ SOMI_API int somi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     if (delta_splits < 1 || (delta_splits > 1 && delta_dtype != SOMI_F32)) return SOMI_ERR_UNSUPPORTED;
     const size_t smem = static_cast<size_t>(H) * sizeof(float);
     if (smem > 200 * 1024) return SOMI_ERR_UNSUPPORTED;
-    // few rows of a wide model: spread each row over a cluster of CTAs
-    int cluster = 0;
-    if (n_out <= 32 && (H & 3) == 0) {
-        if (H >= 2048 && H % 32 == 0) cluster = 8;
-        else if (H >= 512 && H % 16 == 0) cluster = 4;
-    }
-    if (cluster) {
-        const int cols = H / cluster;                        // a multiple of 4
-        const size_t csmem = static_cast<size_t>(cols) * sizeof(float);
-        const int cthreads = cols >= 1024 ? 256 : 128;
-#define SOMI_LAUNCH_CNORM(TD, TO)                                                                \
-    launch_pdl_cluster(add_rmsnorm_cluster_kernel<TD, TO>, dim3(n_out * cluster), dim3(cthreads), \
-                       csmem, stream, cluster, residual, static_cast<const TD*>(delta),          \
-                       delta_splits, delta_split_stride, weight, weight_dtype, eps,              \
-                       static_cast<TO*>(out), rows, H, write_back, cols)
-        if (delta_dtype == SOMI_F32 && out_dtype == SOMI_F32) SOMI_LAUNCH_CNORM(float, float);
-        else if (delta_dtype == SOMI_BF16 && out_dtype == SOMI_BF16) SOMI_LAUNCH_CNORM(__nv_bfloat16, __nv_bfloat16);
-        else if (delta_dtype == SOMI_F32 && out_dtype == SOMI_BF16) SOMI_LAUNCH_CNORM(float, __nv_bfloat16);
-        else SOMI_LAUNCH_CNORM(__nv_bfloat16, float);
-#undef SOMI_LAUNCH_CNORM
-        return launch_status();
-    }
-    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    // Few rows (a decode step): the step waits for this kernel, so a row is read in one pass with a
+    // thread per four columns.  (A thread-block cluster per row, with the sum of squares through
+    // distributed shared memory, was slower: its two cluster barriers cost more than they saved.)
+    // Many rows: fewer threads per row, more rows per SM.
+    int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    if (n_out <= 32 && (H & 3) == 0) threads = min(1024, ((H / 4 + 31) / 32) * 32);
 #define SOMI_LAUNCH_NORM(TD, TO)                                                                 \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
