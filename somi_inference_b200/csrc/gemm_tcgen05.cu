@@ -129,11 +129,18 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
     }
     pdl_wait();
 
+    // The activation tiles of the stages that already hold their weights: a thread issues a copy
+    // every hundred-odd cycles, so the epilogue warps, idle until the accumulator is complete,
+    // share them with the producer.
+    if (lane == 0 && (warp == 0 || warp >= 2) && warp != 6) {
+        const int w5 = warp == 0 ? 0 : warp - 1;           // 0..4
+        for (int kb = w5; kb < n_pre; kb += 5)
+            tma_load_2d(smem_u32(stages + kb * StageBytes + kGemmWBytes), &x_map,
+                        (kb0 + kb) * kGemmBK, 0, smem_u32(&full_bar[kb]));
+    }
+    __syncwarp();          // the other lanes do not run ahead into a polling loop meanwhile
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < n_pre; ++kb)
-                tma_load_2d(smem_u32(stages + kb * StageBytes + kGemmWBytes), &x_map,
-                            (kb0 + kb) * kGemmBK, 0, smem_u32(&full_bar[kb]));
             for (int kb = n_pre; kb < nkb; ++kb) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
@@ -223,8 +230,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                 const int half_n = N >> 1;
 #pragma unroll
                 for (int m = 0; m < TOK; ++m) {
+                    if (m >= M) break;                      // uniform: M is a kernel argument
                     const float other = __shfl_xor_sync(0xffffffffu, acc[m], 1);
-                    if ((lane & 1) == 0 && n < N && m < M) {
+                    if ((lane & 1) == 0 && n < N) {
                         const float g = acc[m];
                         y[static_cast<size_t>(m) * half_n + (n >> 1)] =
                             __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * other);
