@@ -127,6 +127,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
             tma_load_2d(smem_u32(stages + kb * StageBytes), &w_map, (kb0 + kb) * kGemmBK, n0, fb);
         }
     }
+    // The barriers of those stages are armed with their byte counts now.  Other warps will issue
+    // copies that complete on them: a copy must not complete on a barrier before its bytes have
+    // been announced (the count would pass below zero), so everyone meets here first.
+    __syncthreads();
     pdl_wait();
 
     // The activation tiles of the stages that already hold their weights: a thread issues a copy
@@ -138,7 +142,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
             tma_load_2d(smem_u32(stages + kb * StageBytes + kGemmWBytes), &x_map,
                         (kb0 + kb) * kGemmBK, 0, smem_u32(&full_bar[kb]));
     }
-    __syncwarp();          // the other lanes do not run ahead into a polling loop meanwhile
+    __syncwarp();
     if (warp == 0) {
         if (lane == 0) {
             for (int kb = n_pre; kb < nkb; ++kb) {
