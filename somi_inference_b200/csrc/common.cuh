@@ -64,6 +64,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return r;
 }
 
+// The rotation of a pair (a at dim i, b at dim i + rot/2) by (cos, sin), with the roundings
+// spelled out so that every kernel that rotates gives the same bits.
+__device__ __forceinline__ float rope_lo(float a, float b, float c, float s) {
+    return __fmaf_rn(a, c, -__fmul_rn(b, s));
+}
+__device__ __forceinline__ float rope_hi(float a, float b, float c, float s) {
+    return __fmaf_rn(b, c, __fmul_rn(a, s));
+}
+
 inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 
 // ---- programmatic dependent launch

@@ -170,8 +170,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
             T* x = row + static_cast<size_t>(head) * hd;
             const F2 a = load2(x + i), b = load2(x + i + half);
             const float c0 = cs[i], c1 = cs[i + 1], s0 = cs[half + i], s1 = cs[half + i + 1];
-            const float o1x = a.x * c0 - b.x * s0, o1y = a.y * c1 - b.y * s1;
-            const float o2x = b.x * c0 + a.x * s0, o2y = b.y * c1 + a.y * s1;
+            const float o1x = rope_lo(a.x, b.x, c0, s0), o1y = rope_lo(a.y, b.y, c1, s1);
+            const float o2x = rope_hi(a.x, b.x, c0, s0), o2y = rope_hi(a.y, b.y, c1, s1);
             store2(x + i, o1x, o1y);
             store2(x + i + half, o2x, o2y);
             if (slot >= 0 && head >= nq) {
@@ -186,8 +186,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
             T* x = row + static_cast<size_t>(head) * hd;
             const float a = to_float(x[i]), b = to_float(x[i + half]);
             const float c = cs[i], s = cs[half + i];
-            const T o1 = from_float<T>(a * c - b * s);
-            const T o2 = from_float<T>(b * c + a * s);
+            const T o1 = from_float<T>(rope_lo(a, b, c, s));
+            const T o2 = from_float<T>(rope_hi(a, b, c, s));
             x[i] = o1;
             x[i + half] = o2;
             if (slot >= 0 && head >= nq) {
@@ -286,8 +286,8 @@ rope_store_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict_
             const float* sn = c + half;
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-                o1[k] = a[k] * c[k] - b[k] * sn[k];
-                o2[k] = b[k] * c[k] + a[k] * sn[k];
+                o1[k] = rope_lo(a[k], b[k], c[k], sn[k]);
+                o2[k] = rope_hi(a[k], b[k], c[k], sn[k]);
             }
             const uint4 r1 = pack8(o1), r2 = pack8(o2);
             *reinterpret_cast<uint4*>(x + i) = r1;
@@ -373,8 +373,8 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const float c = cs[i + k], s = cs[half + i + k];
-                o1.v[k] = a.v[k] * c - b.v[k] * s;
-                o2.v[k] = b.v[k] * c + a.v[k] * s;
+                o1.v[k] = rope_lo(a.v[k], b.v[k], c, s);
+                o2.v[k] = rope_hi(a.v[k], b.v[k], c, s);
             }
             __nv_bfloat16* dst = head < nq
                 ? qrow + head * hd
@@ -403,8 +403,8 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
         const int head = h0 + idx / half, i = idx % half;
         const float a = value(head * hd + i), b = value(head * hd + i + half);
         const float c = cs[i], s = cs[half + i];
-        const __nv_bfloat16 o1 = __float2bfloat16_rn(a * c - b * s);
-        const __nv_bfloat16 o2 = __float2bfloat16_rn(b * c + a * s);
+        const __nv_bfloat16 o1 = __float2bfloat16_rn(rope_lo(a, b, c, s));
+        const __nv_bfloat16 o2 = __float2bfloat16_rn(rope_hi(a, b, c, s));
         if (head < nq) {
             qrow[head * hd + i] = o1;
             qrow[head * hd + i + half] = o2;
