@@ -60,3 +60,27 @@ def test_skinny_gemm_swiglu(ops, M, I, K):
     gg, uu = x.float() @ gate.float().T, x.float() @ up.float().T
     ref = gg * torch.sigmoid(gg) * uu
     torch.testing.assert_close(y.float(), ref, rtol=1.6e-2, atol=1e-2 * max(ref.abs().max().item(), 1.0))
+
+
+@pytest.mark.parametrize("M,N,K", [(17, 18992, 896), (17, 896, 896), (8, 18992, 896), (8, 1152, 896),
+                                   (64, 18992, 896), (64, 896, 4864)])
+def test_skinny_gemm_launched_alone_many_times(ops, M, N, K):
+    """Each launch on an idle GPU, with nothing before it to wait for: the warps that wait for the
+    preceding kernel pass that wait at once, which is when an unordered hand-over between the
+    kernel's warps would show (every ring depth and token width of the kernel is among the cases)."""
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    ref = x.float() @ w.float().T
+    scale = max(ref.abs().max().item(), 1.0)
+    first = None
+    for i in range(40):
+        torch.cuda.synchronize()
+        y = ops.skinny_gemm(x, w, None, ops.GEMM_F32)
+        torch.cuda.synchronize()
+        if first is None:
+            first = y.clone()
+            assert (y - ref).abs().max().item() <= 2e-5 * scale * (K / 64) ** 0.5
+        else:
+            assert torch.equal(y, first), f"launch {i} differs from the first"
+    ops.check_errors()
