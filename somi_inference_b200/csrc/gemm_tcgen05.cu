@@ -78,6 +78,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
                    const __grid_constant__ CUtensorMap x_map, int M, int N, int K,
                    int kb_per_split, int mode, const void* __restrict__ bias, int bias_dtype,
                    void* __restrict__ out, long long out_split_stride) {
+    // The two MMA threads take the K blocks in turn.  With an even number of stages each stage
+    // belongs to one of them for good, and that thread sees every phase of the stage's barrier in
+    // order.  With an odd number a stage would alternate between the threads: a thread could meet
+    // a barrier for the first time in its second phase, before the first has completed, and a
+    // parity wait cannot tell "not yet" from "done" then (it passed at once, the thread multiplied
+    // the wrong tile and released the stage under the other thread: wrong sums, run-out waits,
+    // once a launch failure, until this was found).
+    static_assert(STAGES % 2 == 0, "the ring depth must be even: see the comment");
     constexpr int XBytes = TOK * kGemmBK * 2;
     constexpr int StageBytes = kGemmWBytes + XBytes;
     constexpr int TmemCols = 2 * TOK < 32 ? 32 : 2 * TOK;     // one accumulator per MMA thread
@@ -315,14 +323,14 @@ SOMI_API int somi_skinny_gemm(const void* w_map, const void* x_map, int x_box_ro
     const CUtensorMap* wm = static_cast<const CUtensorMap*>(w_map);
     const CUtensorMap* xm = static_cast<const CUtensorMap*>(x_map);
     const long long stride = static_cast<long long>(M) * N;
-    // deep_ring: one CTA per SM with an 8-stage ring; otherwise two CTAs per SM with 4 to 6
-    // stages each (what fits twice into shared memory), so that one CTA's prologue and epilogue
-    // overlap the other's main loop.
+    // deep_ring: one CTA per SM with an 8-stage ring; otherwise two CTAs per SM with 4 or 6
+    // stages each (an even number that fits twice into shared memory), so that one CTA's prologue
+    // and epilogue overlap the other's main loop.
 #define SOMI_SKINNY(TOK, ST) \
     return launch_skinny<TOK, ST>(wm, xm, M, N, K, splits, mode, bias, bias_dtype, out, stride, stream)
     switch (x_box_rows) {
         case 16: if (deep_ring) SOMI_SKINNY(16, 8); else SOMI_SKINNY(16, 6);
-        case 32: if (deep_ring) SOMI_SKINNY(32, 8); else SOMI_SKINNY(32, 5);
+        case 32: if (deep_ring) SOMI_SKINNY(32, 8); else SOMI_SKINNY(32, 4);
         case 64: if (deep_ring) SOMI_SKINNY(64, 8); else SOMI_SKINNY(64, 4);
         default: return SOMI_ERR_UNSUPPORTED;
     }

@@ -63,7 +63,7 @@ def test_skinny_gemm_swiglu(ops, M, I, K):
 
 
 @pytest.mark.parametrize("M,N,K", [(17, 18992, 896), (17, 896, 896), (8, 18992, 896), (8, 1152, 896),
-                                   (64, 18992, 896), (64, 896, 4864)])
+                                   (64, 18992, 896), (64, 896, 4864), (24, 19000, 2048)])
 def test_skinny_gemm_launched_alone_many_times(ops, M, N, K):
     """Each launch on an idle GPU, with nothing before it to wait for: the warps that wait for the
     preceding kernel pass that wait at once, which is when an unordered hand-over between the
