@@ -8,17 +8,19 @@
 // second product, so the cache's [key][dim] rows are used as they are), P written by the
 // softmax warps.  Keys and values have rings of their own: a key tile is free again as soon as
 // its scores are computed, a value tile only after the second product, so the keys can be
-// fetched two tiles ahead with two stages.  Warp roles: warp 0 producer (TMA), warp 1 MMA
-// issuer, warps 2-9 softmax: a query row is one lane of tensor memory and is served by two
-// threads (one per 64 of a tile's 128 keys) that agree on the row maximum through shared
-// memory.  The output accumulates in tensor memory across key tiles; it is rescaled there
-// (tcgen05.ld / tcgen05.st) only when a row's maximum grows by more than 2^8, otherwise the old
+// fetched two tiles ahead with two stages.  Warp roles: warp 0 key producer (TMA), warp 1 MMA
+// issuer, warps 2-9 softmax, warp 10 value producer.  A query row is one lane of tensor memory
+// and is served by two threads, one per 64 of a tile's 128 keys; each half keeps its own
+// maximum and sum and has its own output accumulator in tensor memory (O_lo += P_lo V_lo,
+// O_hi += P_hi V_hi), and the two are added at the end like the parts of a split over the keys,
+// so the halves exchange nothing per tile.  An accumulator is rescaled in tensor memory
+// (tcgen05.ld / tcgen05.st) only when its row maximum grows by more than 2^8, otherwise the old
 // maximum keeps serving as the reference (probabilities up to 256 are harmless in float32 sums
 // and bfloat16 operands), so most tiles cost the softmax warps one pass over S and one over P.
-// A tile's fixed costs (barrier tests, tensor-memory load latency, the exchange of maxima, the
-// proxy fence) are paid once per 128 keys: with 64-key tiles the same kernel took 1.5 times as
-// long.  Softmax is float32, base 2.  Every wait on an mbarrier is bounded and failure is
-// recorded in an error word.
+// A tile's fixed costs (barrier tests, tensor-memory load latency, the proxy fence) are paid
+// once per 128 keys: with 64-key tiles the same kernel took 1.5 times as long.  Softmax is
+// float32, base 2.  Every wait on an mbarrier is bounded and failure is recorded in an error
+// word.
 //
 // The reference's prefill kernel (somi_inference/core/flash_attention_triton.py:31-194) is a
 // FlashAttention-2 loop on `tl.dot`; formulas in somi_inference/models/qwen2.py:158-186.
@@ -145,10 +147,9 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     unsigned char* Vs = Ks + STAGES * TILE;           // STAGES tiles
     unsigned char* Ps = Vs + STAGES * TILE;           // two buffers of two [128 rows][64 keys] blocks
     __shared__ __align__(8) unsigned long long q_full, k_full[kFaMaxStages], k_empty[kFaMaxStages],
-        v_full[kFaMaxStages], v_empty[kFaMaxStages], s_full[2], p_full[2], pv_full[2];
+        v_full[kFaMaxStages], v_empty[kFaMaxStages], s_full[2], p_full[2][2], pv_full[2][2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
-    __shared__ float xmax_s[2][kFaBM];       // exchanged between the two warps that share a row
 
     pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -162,8 +163,10 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(smem_u32(&s_full[s]), 1);
-            mbar_init(smem_u32(&p_full[s]), 8);          // one arrival per softmax warp
-            mbar_init(smem_u32(&pv_full[s]), 1);
+            for (int h = 0; h < 2; ++h) {
+                mbar_init(smem_u32(&p_full[h][s]), 4);   // one arrival per softmax warp of the half
+                mbar_init(smem_u32(&pv_full[h][s]), 1);
+            }
         }
         mbar_fence_init();
         failed_s = 0;
@@ -184,7 +187,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     fa_fence_after();
     pdl_wait();
     const uint32_t tmem_s = tmem_base_s;                 // S buffers at columns 0 and 128
-    const uint32_t tmem_pv = tmem_base_s + 2 * kFaBN;
+    const uint32_t tmem_pv = tmem_base_s + 2 * kFaBN;    // O of key half 0, then O of key half 1
 
     // Later tiles of a prompt see more keys.  Blocks are handed out longest first (heads
     // first, last tile first), so that the short ones fill the end.
@@ -284,16 +287,21 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int st = t % STAGES;
                 if (!mbar_wait(smem_u32(&v_full[st]), (t / STAGES) & 1)) { ok = false; break; }
-                if (!mbar_wait(smem_u32(&p_full[t & 1]), (t >> 1) & 1)) { ok = false; break; }
-                fa_fence_after();
-                const uint64_t pd = p_desc + (((t & 1) * 2 * kFaHalf) >> 4);
-                const uint64_t vd = v_desc + ((st * TILE) >> 4);
+                // each half of the tile's keys has its own probabilities, its own output
+                // accumulator and its own pace
 #pragma unroll
-                for (int k16 = 0; k16 < kFaBN / 16; ++k16)
-                    fa_umma(tmem_pv, pd + (((k16 >> 2) * kFaHalf + (k16 & 3) * 32) >> 4),
-                            vd + ((k16 * 16 * 128) >> 4), idesc_pv,
-                            (t > 0 || k16 > 0) ? 1u : 0u);     // O accumulates over the key tiles
-                fa_commit(smem_u32(&pv_full[t & 1]));
+                for (int h = 0; h < 2; ++h) {
+                    if (!mbar_wait(smem_u32(&p_full[h][t & 1]), (t >> 1) & 1)) { ok = false; break; }
+                    fa_fence_after();
+                    const uint64_t pd = p_desc + (((t & 1) * 2 * kFaHalf + h * kFaHalf) >> 4);
+                    const uint64_t vd = v_desc + ((st * TILE + h * 64 * 128) >> 4);
+#pragma unroll
+                    for (int k16 = 0; k16 < 4; ++k16)
+                        fa_umma(tmem_pv + h * HD, pd + ((k16 * 32) >> 4), vd + ((k16 * 16 * 128) >> 4),
+                                idesc_pv, (t > 0 || k16 > 0) ? 1u : 0u);   // accumulates over the tiles
+                    fa_commit(smem_u32(&pv_full[h][t & 1]));
+                }
+                if (!ok) break;
                 fa_commit(smem_u32(&v_empty[st]));
                 if (t + 2 < n_tiles) issue_scores(t + 2);      // S buffer t & 1 has been read
             }
@@ -303,8 +311,13 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             }
         }
     } else if (warp < 10) {
-        // ---- softmax warps: a query row (one lane of tensor memory) is shared by two threads,
-        // one per half of the tile's 128 keys; they agree on the row maximum through shared memory
+        // ---- softmax warps: a query row (one lane of tensor memory) is served by two threads, one
+        // per half of the tile's 128 keys.  The halves are independent: each keeps its own
+        // maximum and sum and feeds its own output accumulator, and the two results are added
+        // at the end like the partial results of a split over the keys.  So the halves do not
+        // meet in every tile.  (Starting them half a tile apart, so that one half's exp2 phase
+        // would run beside the other's loads, changed nothing: both wait for the same scores,
+        // which are issued when the later half is done with a tile.)
         const int q = warp & 3;                                  // lane quarter this warp may access
         const int half = (warp - 2) >> 2;                        // which 64 keys of a tile
         const int row = q * 32 + lane;
@@ -316,6 +329,7 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         const unsigned span = static_cast<unsigned>(pos - lo);
         float m = -INFINITY, l = 0.f;        // m: the reference maximum in use (log2 units)
         bool ok = true;
+        const uint32_t tmem_o = tmem_pv + half * HD;         // this half's output accumulator
         for (int t = 0; t < n_tiles; ++t) {
             ok = mbar_wait(smem_u32(&s_full[t & 1]), (t >> 1) & 1, ok ? 400000 : 1) && ok;
             fa_fence_after();
@@ -340,14 +354,11 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 sv[j] = x;
                 mx[j & 3] = fmaxf(mx[j & 3], x);
             }
-            float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            xmax_s[half][row] = tmax;
-            fa_pair_sync(1 + q);
             // the scale is positive, so the maximum is taken over the raw scores and scaled once
-            tmax = fmaxf(tmax, xmax_s[half ^ 1][row]) * scale_log2e;
-            // This tile's P buffer was last read by the product of tile t - 2.  That product was
+            const float tmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2e;
+            // This tile's P buffer was last read by the products of tile t - 2.  They were
             // issued before the scores of tile t, and a commit covers everything issued before
-            // it, so the wait for S(t) has covered it already.
+            // it, so the wait for S(t) has covered them already.
             // keep the old reference maximum unless the new one is more than 2^8 above it
             float alpha = 1.f;
             bool rescale = false;
@@ -359,14 +370,14 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                 rescale = true;
             }
             if (__any_sync(0xffffffffu, rescale)) {
-                // O of the tiles so far must be complete before it is rescaled in tensor memory;
-                // each of the two threads of a row rescales one half of the columns
-                if (t >= 1) ok = mbar_wait(smem_u32(&pv_full[(t - 1) & 1]), ((t - 1) >> 1) & 1, ok ? 400000 : 1) && ok;
+                // this half's O of the tiles so far must be complete before it is rescaled in
+                // tensor memory
+                if (t >= 1) ok = mbar_wait(smem_u32(&pv_full[half][(t - 1) & 1]), ((t - 1) >> 1) & 1, ok ? 400000 : 1) && ok;
                 fa_fence_after();
 #pragma unroll
-                for (int c = 0; c < HD / 64; ++c) {
+                for (int c = 0; c < HD / 32; ++c) {
                     float v[32];
-                    const uint32_t a = tmem_pv + lane_addr + half * (HD / 2) + c * 32;
+                    const uint32_t a = tmem_o + lane_addr + c * 32;
                     fa_tmem_ld32(a, v);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] *= alpha;
@@ -397,31 +408,42 @@ paged_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
             fa_fence_before();
             fence_proxy_async();                // P is read by the tensor core (async proxy)
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&p_full[t & 1]));
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[half][t & 1]));
         }
-        // ---- the output: O / l from tensor memory; each thread writes half of its row
-        fa_pair_sync(1 + q);             // the partner has read this tile's maximum
-        xmax_s[half][row] = l;
-        fa_pair_sync(1 + q);
-        l += xmax_s[half ^ 1][row];
+        // ---- the output: the two halves' results added up; each thread writes half of its row
         const int last = n_tiles - 1;
-        ok = mbar_wait(smem_u32(&pv_full[last & 1]), (last >> 1) & 1, ok ? 400000 : 1) && ok;
+        ok = mbar_wait(smem_u32(&pv_full[half][last & 1]), (last >> 1) & 1, ok ? 400000 : 1) && ok;
+        // (maximum, sum) of the two halves meet in the Q tile's place: every product that reads Q
+        // was issued, and has completed, before the last product of either half
+        float2* ml_s = reinterpret_cast<float2*>(Qs);
+        ml_s[half * kFaBM + row] = make_float2(m, l);
+        // the partner's accumulator is complete, and its maximum and sum are in shared memory
+        fa_fence_before();
+        fa_pair_sync(1 + q);
         fa_fence_after();
         if (!ok) failed_s = 1;
-        const float inv = 1.0f / l;
+        const float2 other = ml_s[(half ^ 1) * kFaBM + row];
+        const float m_o = other.x, l_o = other.y;
+        // a half in which the row saw no key has maximum -inf and sum 0
+        const float mm = fmaxf(m, m_o);
+        const float w_me = m == -INFINITY ? 0.f : fast_exp2(m - mm);
+        const float w_ot = m_o == -INFINITY ? 0.f : fast_exp2(m_o - mm);
+        const float inv = 1.0f / (w_me * l + w_ot * l_o);
+        const float a_me = w_me * inv, a_ot = w_ot * inv;
         __nv_bfloat16* dst = out + static_cast<size_t>(row0 + row) * nq * HD + head * HD + half * (HD / 2);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c) {
-            float v[32];
-            fa_tmem_ld32(tmem_pv + lane_addr + half * (HD / 2) + c * 32, v);
+            float v[32], u[32];
+            fa_tmem_ld32(tmem_o + lane_addr + half * (HD / 2) + c * 32, v);
+            fa_tmem_ld32(tmem_pv + (half ^ 1) * HD + lane_addr + half * (HD / 2) + c * 32, u);
             if (row < rows) {
 #pragma unroll
                 for (int d = 0; d < 32; d += 8) {
                     uint4 w;
-                    w.x = pack_bf16(v[d] * inv, v[d + 1] * inv);
-                    w.y = pack_bf16(v[d + 2] * inv, v[d + 3] * inv);
-                    w.z = pack_bf16(v[d + 4] * inv, v[d + 5] * inv);
-                    w.w = pack_bf16(v[d + 6] * inv, v[d + 7] * inv);
+                    w.x = pack_bf16(v[d] * a_me + u[d] * a_ot, v[d + 1] * a_me + u[d + 1] * a_ot);
+                    w.y = pack_bf16(v[d + 2] * a_me + u[d + 2] * a_ot, v[d + 3] * a_me + u[d + 3] * a_ot);
+                    w.z = pack_bf16(v[d + 4] * a_me + u[d + 4] * a_ot, v[d + 5] * a_me + u[d + 5] * a_ot);
+                    w.w = pack_bf16(v[d + 6] * a_me + u[d + 6] * a_ot, v[d + 7] * a_me + u[d + 7] * a_ot);
                     *reinterpret_cast<uint4*>(dst + c * 32 + d) = w;
                 }
             }
