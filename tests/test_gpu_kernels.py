@@ -367,3 +367,30 @@ def test_silu_mul_interleaved(ops, dtype, T, I):
     ref = torch.empty(T, I, dtype=dtype)
     HOST.silu_mul(gu, ref, interleaved=True)
     torch.testing.assert_close(out.cpu().float(), ref.float(), **tol(dtype))
+
+
+@pytest.mark.parametrize("nq,nkv,hd,reqs", [
+    (4, 2, 128, [(300, 200), (0, 129)]),          # prompt portions: the tcgen05 kernel
+    (6, 2, 64, [(0, 300), (100, 64)]),
+    (14, 2, 64, [(2047, 1), (128, 1), (5, 1)]),    # single tokens: the split-KV kernel and its merge
+    (8, 4, 128, [(1000, 1), (127, 1)]),
+])
+def test_attention_launched_alone_many_times(ops, nq, nkv, hd, reqs):
+    """Each launch on an idle GPU with a synchronisation before and after: whatever a kernel's
+    warps hand to one another without an order would show as a result that changes from launch
+    to launch, or as a wait that runs out."""
+    mgr, batch, qkv, view, _ = attention_case(ops, nq=nq, nkv=nkv, hd=hd, page_size=16, window=None,
+                                              requests=reqs, dtype=torch.bfloat16, seed=21)
+    first = None
+    for i in range(30):
+        out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
+        ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
+                            hd ** -0.5, None, out, storage=view.storage)
+        torch.cuda.synchronize()
+        if first is None:
+            first = out.clone()
+            assert not torch.isnan(first.float()).any()
+        else:
+            assert torch.equal(out, first), f"launch {i} differs from the first"
+    ops.check_errors()
