@@ -298,7 +298,8 @@ def main() -> int:
     dt = time.perf_counter() - t0
     n1 = sum(len(r.output_tokens) for r in e2e_reqs)
     e2e = {"value": round((n1 - n0) / dt, 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": int(llm.engine.builder.h2d_bytes_last + llm.sampler_h2d_bytes()),
+           "h2d_bytes_per_step": int(llm.engine.builder.h2d_bytes_last + llm.sampler_h2d_bytes()
+                                     + llm.engine.token_patch_bytes),
            "d2h_bytes_per_step": int(llm.d2h_bytes_last), "ms_per_step": round(dt / args.steps * 1e3, 3)}
     for r in e2e_reqs:
         if llm.engine.has(r.request_id):

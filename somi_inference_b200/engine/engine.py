@@ -92,6 +92,8 @@ class Engine:
         self.last_batch: StepBatch | None = None
         self.use_graphs = use_graphs
         self.max_graphs = 64
+        self._token_stage = None
+        self.token_patch_bytes = 0
         self.graph_max_tokens = 8192     # larger steps are bound by the GPU, not by the host
         self._graphs: dict[tuple, tuple] = {}
         self._seen: dict[tuple, int] = {}
@@ -181,6 +183,27 @@ class Engine:
             self._graphs[key] = (graph, static_logits, self.ops.launches - before)
             self.ops.launches = before
         return logits
+
+    def prebuild(self, entries: Sequence[StepEntry]) -> StepBatch:
+        """The batch descriptor of a step whose token ids are not known yet (`entries` carry
+        placeholders): built and uploaded now, run later by `run_prebuilt`.  No other step may
+        be built in between; the requests' pages are reserved by the caller."""
+        batch, _ = self.builder.build(entries)
+        return batch
+
+    def run_prebuilt(self, batch: StepBatch, token_ids: Sequence[int], keep: bool = True) -> torch.Tensor:
+        """Run a batch from `prebuild` with its token ids, one per token of the batch in the
+        entries' order (single-token requests only, so that order is the batch's order)."""
+        n = len(token_ids)
+        if n != batch.num_tokens or batch.num_prefill_requests:
+            raise ValueError("run_prebuilt takes one token id for every single-token request")
+        if self._token_stage is None or self._token_stage.numel() < n:
+            self._token_stage = torch.empty(max(n, 256), dtype=torch.int32,
+                                            pin_memory=self.device.type == "cuda")
+        self._token_stage[:n] = torch.as_tensor(token_ids, dtype=torch.int32)
+        batch.token_ids.copy_(self._token_stage[:n], non_blocking=True)
+        self.token_patch_bytes = 4 * n
+        return self._run(batch, keep)
 
     def end(self, request: object) -> None:
         """The request is finished: everything it holds goes back to the pools."""

@@ -61,6 +61,8 @@ class LLM:
         self._model_dir = model
         self.steps_run = 0
         self.d2h_bytes_last = 0
+        self.prepare_early = True      # prepare the next decode step while the GPU runs this one
+        self._early = None             # (scheduled batch, its descriptor) prepared for the next step
 
     def sampler_h2d_bytes(self) -> int:
         return self.sampler.h2d_bytes_last
@@ -88,36 +90,63 @@ class LLM:
 
     # ------------------------------------------------------------------- loop
     def step(self) -> list[Request]:
-        """One scheduling step and one model step; returns the requests that finished in it."""
-        batch = self.scheduler.schedule()
-        if not batch.items:
-            if self.scheduler.has_unfinished() and not batch.preempted:
-                raise RuntimeError("nothing can be scheduled: the cache is too small for the "
-                                   "request at the head of the queue")
-            return []
-        entries = []
-        samplers = []
-        for item in batch.items:
-            toks = item.request.tokens(item.start, item.num_tokens)
-            entries.append(StepEntry(item.request.request_id, toks,
-                                     [item.num_tokens - 1] if item.samples else []))
-            if item.samples:
-                samplers.append(item.request)
-        logits = self.engine.run_reserved(entries, keep=False)     # sampled from at once
+        """One scheduling step and one model step; returns the requests that finished in it.
+
+        While the GPU runs a step of single decode tokens, the next step is prepared as far as
+        it does not depend on the tokens being sampled: the scheduler's decision, the pages and
+        the batch descriptor (`Scheduler.continue_decoding`, `Engine.prebuild`).  When the tokens
+        are there, only their ids are copied in.  If a request ends on its token, or a new one
+        has arrived, the preparation is given back and the step is scheduled the usual way.
+        """
+        early, self._early = self._early, None
+        if early is not None and not self.scheduler.still_valid(early[0]):
+            self.scheduler.abandon(early[0])
+            early = None
+        if early is not None:
+            batch, prepared = early
+            samplers = [item.request for item in batch.items]
+            logits = self.engine.run_prebuilt(prepared, [r.output_tokens[-1] for r in samplers],
+                                              keep=False)
+        else:
+            batch = self.scheduler.schedule()
+            if not batch.items:
+                if self.scheduler.has_unfinished() and not batch.preempted:
+                    raise RuntimeError("nothing can be scheduled: the cache is too small for the "
+                                       "request at the head of the queue")
+                return []
+            entries = []
+            samplers = []
+            for item in batch.items:
+                toks = item.request.tokens(item.start, item.num_tokens)
+                entries.append(StepEntry(item.request.request_id, toks,
+                                         [item.num_tokens - 1] if item.samples else []))
+                if item.samples:
+                    samplers.append(item.request)
+            logits = self.engine.run_reserved(entries, keep=False)     # sampled from at once
         sampled: dict[int, int] = {}
+        ids = None
         if samplers:
             ids = self.sampler.sample(
                 logits, [r.sampling_params for r in samplers],
                 [len(r.output_tokens) for r in samplers], [r.seed for r in samplers],
                 [r.all_tokens if r.sampling_params.repetition_penalty != 1.0 else ()
                  for r in samplers])
+        # the GPU is busy with the step: the host's part of the next one
+        self.scheduler.advance(batch)
+        if self.prepare_early and len(samplers) == len(batch.items):
+            nxt = self.scheduler.continue_decoding()
+            if nxt is not None:
+                prepared = self.engine.prebuild(
+                    [StepEntry(item.request.request_id, [0], [0]) for item in nxt.items])
+                self._early = (nxt, prepared)
+        if ids is not None:
             host = ids.cpu()
             self.d2h_bytes_last = host.numel() * host.element_size()
             sampled = {r.request_id: int(t) for r, t in zip(samplers, host.tolist())}
         self.steps_run += 1
         if self.steps_run % 256 == 0 and hasattr(self.engine.ops, "check_errors"):
             self.engine.ops.check_errors()
-        return self.scheduler.update(batch, sampled)
+        return self.scheduler.update(batch, sampled, advanced=True)
 
     def run(self, requests: Sequence[tuple[int, Request]]) -> list[Request]:
         """Run until all `(arrival_step, request)` pairs are finished

@@ -208,18 +208,66 @@ class Scheduler:
             budget -= n
         return ScheduledBatch(items, preempted, admitted)
 
+    # ------------------------------------------------- the next step, early
+    def advance(self, batch: ScheduledBatch) -> None:
+        """The part of `update` that needs no sampled token: the step's tokens are in the cache."""
+        for item in batch.items:
+            self.cache.commit(item.request.request_id)
+            item.request.num_computed += item.num_tokens
+
+    def continue_decoding(self) -> ScheduledBatch | None:
+        """The next step's schedule, decided while the tokens of this step are still being
+        sampled, for the one state in which it does not depend on them: nobody waits, and every
+        running request has just had its last known token computed and cannot finish by length
+        on the token that is about to arrive.  `schedule()` would then give every running request
+        one decode token, in order, and nothing else; that is what is reserved and returned here.
+        None where the state is another one, or where a page is missing (then `schedule()`
+        decides, with preemption if it must).  Call after `advance`; if a request finishes on
+        the arriving token after all (end of sequence), `abandon` the batch.
+        """
+        if self.waiting or not self.running or len(self.running) > self.max_num_batched_tokens:
+            return None
+        for req in self.running:
+            if req.num_computed != req.num_tokens or len(req.output_tokens) + 1 >= req.max_new_tokens:
+                return None
+        reserved: list[Request] = []
+        try:
+            for req in self.running:
+                self.cache.reserve(req.request_id, 1)
+                reserved.append(req)
+        except OutOfPages:
+            for req in reserved:
+                self.cache.cancel(req.request_id)
+            return None
+        # the token itself sits at index num_computed once it has arrived
+        return ScheduledBatch([ScheduledItem(r, r.num_computed, 1, True) for r in self.running], [], [])
+
+    def still_valid(self, batch: ScheduledBatch) -> bool:
+        """Whether a batch from `continue_decoding` is what `schedule()` would decide now."""
+        return (not self.waiting and len(batch.items) == len(self.running)
+                and all(i.request is r for i, r in zip(batch.items, self.running)))
+
+    def abandon(self, batch: ScheduledBatch) -> None:
+        """Give back what `continue_decoding` reserved (requests that ended meanwhile have
+        given everything back already)."""
+        for item in batch.items:
+            if self.cache.is_registered(item.request.request_id):
+                self.cache.cancel(item.request.request_id)
+
     # ----------------------------------------------------------------- update
-    def update(self, batch: ScheduledBatch, sampled: dict[int, int]) -> list[Request]:
-        """After the step: advance, append sampled tokens, finish and free.
+    def update(self, batch: ScheduledBatch, sampled: dict[int, int],
+               advanced: bool = False) -> list[Request]:
+        """After the step: advance (unless `advance` was called already), append sampled
+        tokens, finish and free.
 
         `sampled` maps request_id to the token sampled for every item with
         `samples`.  Returns the requests that finished in this step.
         """
         done: list[Request] = []
+        if not advanced:
+            self.advance(batch)
         for item in batch.items:
             req = item.request
-            self.cache.commit(req.request_id)
-            req.num_computed += item.num_tokens
             if not item.samples:
                 continue
             token = int(sampled[req.request_id])

@@ -49,6 +49,33 @@ def test_temperature_generation_is_reproducible_and_batch_independent(root):
     assert len({tuple(o) for o in together}) == 4
 
 
+def test_end_of_sequence_arrives_while_the_next_step_is_prepared(root):
+    """Generation prepares the next decode step while the tokens of the current one are sampled.
+    A request that ends on such a token (end of sequence, not foreseeable) must not run on, the
+    others must go on unchanged, and every page must come back.  The end-of-sequence token is
+    chosen as one that greedy generation does produce, at different steps in different requests."""
+    from somi_inference_b200 import LLM, SamplingParams
+    d = make_model("B", root, torch.float32, std=STD)
+    cfg, w = plain.load_folder(d)
+    prompts = [random_tokens(n, cfg["vocab_size"], 200 + i) for i, n in enumerate([7, 19, 33, 12])]
+    free_run = [plain.greedy(cfg, w, p, 24) for p in prompts]
+    eos = free_run[1][9]                     # request 1 ends at its 10th token at the latest
+    want = []
+    for o in free_run:
+        want.append(o[:o.index(eos) + 1] if eos in o else o)
+    for early in (True, False):
+        llm = LLM(d, num_blocks=64, block_size=8, max_concurrent=4, dtype="float32", chunk_size=16,
+                  eos_token_id=eos)
+        llm.prepare_early = early
+        outs = llm.generate_many(prompts, max_new_tokens=24,
+                                 sampling_params=SamplingParams(temperature=0.0))
+        assert outs == want, f"prepare_early={early}"
+        assert any(len(o) < 24 for o in outs)
+        llm.step()                           # gives back what was prepared for a step that never came
+        assert llm.engine.cache.free_pages() == [64] * len(llm.engine.cache.groups)
+        llm.engine.cache.check_consistency()
+
+
 def test_preemption_on_the_gpu_gives_the_same_tokens(root):
     from somi_inference_b200 import LLM, SamplingParams
     d = make_model("A", root, torch.float32, std=STD)

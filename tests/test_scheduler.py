@@ -161,3 +161,91 @@ def test_request_validation():
                 dict(repetition_penalty=0.0)):
         with pytest.raises(ValueError):
             SamplingParams(**bad)
+
+
+def test_the_next_decode_step_decided_early_is_what_schedule_would_decide():
+    """`continue_decoding` after `advance`: the same items and the same pages as `schedule()`
+    gives after `update`, in two schedulers fed the same way."""
+    outs = []
+    for early in (False, True):
+        cache, s = make(num_pages=12, eos=7)
+        for i, n in enumerate([5, 3, 6]):
+            s.add_request(req(i, n, max_new=6))
+        log = []
+        b = s.schedule()
+        nxt = None
+        for step in range(8):
+            toks = {i.request.request_id: 9 for i in b.items if i.samples}
+            if early:
+                s.advance(b)
+                nxt = s.continue_decoding() if all(i.samples for i in b.items) else None
+                s.update(b, toks, advanced=True)
+            else:
+                s.update(b, toks)
+            if not s.has_unfinished():
+                break
+            if nxt is not None and s.still_valid(nxt):
+                b = nxt
+            else:
+                if nxt is not None:
+                    s.abandon(nxt)
+                b = s.schedule()
+            nxt = None
+            log.append(([(i.request.request_id, i.start, i.num_tokens, i.samples) for i in b.items],
+                        cache.free_pages()))
+            cache.check_consistency()
+        outs.append(log)
+    assert outs[0] == outs[1] and len(outs[0]) >= 4
+
+
+def test_early_decision_is_given_back_when_a_request_ends_or_arrives():
+    cache, s = make(num_pages=12, eos=7)
+    s.add_request(req(0, 4, max_new=8))
+    s.add_request(req(1, 4, max_new=8))
+    b = s.schedule()
+    s.advance(b)
+    nxt = s.continue_decoding()
+    assert nxt is not None and [i.request.request_id for i in nxt.items] == [0, 1]
+    assert all(i.num_tokens == 1 and i.samples and i.start == 4 for i in nxt.items)
+    free_with_reservation = cache.free_pages()
+    # request 0 meets the end-of-sequence token on the token that arrives now
+    done = s.update(b, {0: 7, 1: 9}, advanced=True)
+    assert [r.request_id for r in done] == [0] and not s.still_valid(nxt)
+    s.abandon(nxt)
+    cache.check_consistency()
+    b2 = s.schedule()
+    assert [(i.request.request_id, i.start, i.num_tokens) for i in b2.items] == [(1, 4, 1)]
+    s.update(b2, {1: 9})
+    # a request that arrives makes the early decision void as well
+    b3 = s.schedule()
+    s.advance(b3)
+    nxt = s.continue_decoding()
+    assert nxt is not None
+    s.update(b3, {1: 9}, advanced=True)
+    s.add_request(req(2, 3))
+    assert not s.still_valid(nxt)
+    s.abandon(nxt)
+    cache.check_consistency()
+    assert free_with_reservation is not None
+
+
+def test_no_early_decision_when_it_would_depend_on_the_token():
+    cache, s = make(num_pages=12)
+    s.add_request(req(0, 4, max_new=2))
+    s.add_request(req(1, 12, max_new=4))
+    b = s.schedule()                       # request 1 has a portion of its prompt left
+    s.advance(b)
+    assert s.continue_decoding() is None   # not every running request is about to decode
+    s.update(b, {0: 9}, advanced=True)
+    b = s.schedule()
+    s.advance(b)
+    assert s.continue_decoding() is None   # request 0 ends by length on the token that arrives
+    s.update(b, {0: 9, 1: 9}, advanced=True)
+    # no page left for another token: left to schedule(), which may preempt
+    cache2, s2 = make(num_pages=2, page_size=4)
+    s2.add_request(req(0, 4, max_new=4))
+    s2.add_request(req(1, 4, max_new=4))
+    b = s2.schedule()
+    s2.advance(b)
+    assert s2.continue_decoding() is None and cache2.free_pages() == [0]
+    cache2.check_consistency()
