@@ -94,6 +94,7 @@ class BatchBuilder:
         self.width_step = max(1, 512 // cache.page_size)     # table columns come in steps of 512 tokens
         self._capacity = 0
         self._turn = 0
+        self.uploads = 0
         self._decode_views: dict = {}
         self._alloc(capacity_ints)
 
@@ -341,4 +342,5 @@ class BatchBuilder:
             ev.record(self._current_stream())
             self._events[self._turn] = ev
         self._last_bytes = total * 4
+        self.uploads += 1                # the device descriptor now belongs to this build
         return offsets, total

@@ -93,6 +93,7 @@ class Engine:
         self.use_graphs = use_graphs
         self.max_graphs = 64
         self._token_stage = None
+        self._prebuilt = None
         self.token_patch_bytes = 0
         self.graph_max_tokens = 8192     # larger steps are bound by the GPU, not by the host
         self._graphs: dict[tuple, tuple] = {}
@@ -189,7 +190,13 @@ class Engine:
         placeholders): built and uploaded now, run later by `run_prebuilt`.  No other step may
         be built in between; the requests' pages are reserved by the caller."""
         batch, _ = self.builder.build(entries)
+        self._prebuilt = (batch, self.builder.uploads)
         return batch
+
+    def prebuilt_is_current(self, batch: StepBatch) -> bool:
+        """Whether the device still holds this batch's descriptor (no other step was built since)."""
+        return (self._prebuilt is not None and self._prebuilt[0] is batch
+                and self._prebuilt[1] == self.builder.uploads)
 
     def run_prebuilt(self, batch: StepBatch, token_ids: Sequence[int], keep: bool = True) -> torch.Tensor:
         """Run a batch from `prebuild` with its token ids, one per token of the batch in the
@@ -197,6 +204,8 @@ class Engine:
         n = len(token_ids)
         if n != batch.num_tokens or batch.num_prefill_requests:
             raise ValueError("run_prebuilt takes one token id for every single-token request")
+        if not self.prebuilt_is_current(batch):
+            raise RuntimeError("another step was built after this one was prepared")
         if self._token_stage is None or self._token_stage.numel() < n:
             self._token_stage = torch.empty(max(n, 256), dtype=torch.int32,
                                             pin_memory=self.device.type == "cuda")

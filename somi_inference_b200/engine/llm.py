@@ -99,7 +99,8 @@ class LLM:
         has arrived, the preparation is given back and the step is scheduled the usual way.
         """
         early, self._early = self._early, None
-        if early is not None and not self.scheduler.still_valid(early[0]):
+        if early is not None and not (self.scheduler.still_valid(early[0])
+                                      and self.engine.prebuilt_is_current(early[1])):
             self.scheduler.abandon(early[0])
             early = None
         if early is not None:

@@ -76,6 +76,29 @@ def test_end_of_sequence_arrives_while_the_next_step_is_prepared(root):
         llm.engine.cache.check_consistency()
 
 
+def test_a_step_of_another_caller_between_prepared_steps(root):
+    """The engine's step function used directly between two steps of generation overwrites the
+    descriptor that generation had prepared: generation must notice and build its step again."""
+    from somi_inference_b200 import LLM, SamplingParams
+    from somi_inference_b200.engine import StepEntry
+    d = make_model("B", root, torch.float32, std=STD)
+    cfg, w = plain.load_folder(d)
+    prompts = [random_tokens(n, cfg["vocab_size"], 300 + i) for i, n in enumerate([11, 23])]
+    llm = LLM(d, num_blocks=64, block_size=8, max_concurrent=3, dtype="float32", chunk_size=16)
+    reqs = [llm.make_request(p, max_new_tokens=14, sampling_params=SamplingParams(temperature=0.0),
+                             ignore_eos=True) for p in prompts]
+    for r in reqs:
+        llm.scheduler.add_request(r)
+    steps = 0
+    while llm.scheduler.has_unfinished():
+        llm.step()
+        steps += 1
+        if steps % 3 == 0:
+            llm.engine.step([StepEntry("other", random_tokens(5, cfg["vocab_size"], steps), [4])])
+            llm.engine.end("other")
+    assert [r.output_tokens for r in reqs] == [plain.greedy(cfg, w, p, 14) for p in prompts]
+
+
 def test_preemption_on_the_gpu_gives_the_same_tokens(root):
     from somi_inference_b200 import LLM, SamplingParams
     d = make_model("A", root, torch.float32, std=STD)
