@@ -214,6 +214,19 @@ class Engine:
         self.token_patch_bytes = 4 * n
         return self._run(batch, keep)
 
+    def run_prebuilt_fed(self, batch: StepBatch, token_ids: torch.Tensor, keep: bool = True) -> torch.Tensor:
+        """As `run_prebuilt`, with the token ids taken from an int32 device tensor (the sampler's
+        output of the step before): nothing waits for the host to have seen them."""
+        if token_ids.numel() != batch.num_tokens or batch.num_prefill_requests:
+            raise ValueError("run_prebuilt_fed takes one token id for every single-token request")
+        if token_ids.dtype != torch.int32 or token_ids.device != batch.token_ids.device:
+            raise ValueError("token ids must be int32 on the engine's device")
+        if not self.prebuilt_is_current(batch):
+            raise RuntimeError("another step was built after this one was prepared")
+        batch.token_ids.copy_(token_ids, non_blocking=True)
+        self.token_patch_bytes = 0
+        return self._run(batch, keep)
+
     def end(self, request: object) -> None:
         """The request is finished: everything it holds goes back to the pools."""
         self.cache.release(request)

@@ -18,6 +18,7 @@ from __future__ import annotations
 import os
 import random
 from collections import deque
+from dataclasses import dataclass
 from typing import Iterator, Sequence
 
 import torch
@@ -25,11 +26,34 @@ import torch
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .engine import Engine
-from .scheduler import Request, Scheduler
+from .scheduler import Request, RequestStatus, ScheduledBatch, Scheduler
 
 DEFAULT_BLOCK_SIZE = 16        # somi_inference/entrypoints/llm.py:25
 DEFAULT_MAX_CONCURRENT = 16    # somi_inference/entrypoints/llm.py:26
 DEFAULT_NUM_BLOCKS = 256       # somi_inference/entrypoints/llm.py:62
+
+
+class _NoEvent:
+    """Stands in for a CUDA event where the engine's device has no streams."""
+
+    def record(self) -> None:
+        pass
+
+    def synchronize(self) -> None:
+        pass
+
+
+@dataclass
+class _Launched:
+    """A step that has been launched and whose sampled ids have not been read yet."""
+
+    batch: ScheduledBatch
+    samplers: list            # the requests that sample in it, in the order of the ids
+    ids: "torch.Tensor | None"         # int32 on the device, one per sampler of the launch
+    host: "torch.Tensor | None"        # the pinned copy that `event` guards
+    event: object
+    rows: list                # for each sampler its row among the launch's ids
+    whole: bool               # no request of the launch has ended since
 
 
 class LLM:
@@ -63,6 +87,11 @@ class LLM:
         self.d2h_bytes_last = 0
         self.prepare_early = True      # prepare the next decode step while the GPU runs this one
         self._early = None             # (scheduled batch, its descriptor) prepared for the next step
+        self.run_ahead = True          # launch the next decode step before the host has the ids
+        self._ahead: _Launched | None = None       # the step that was launched ahead
+        self._ids_host = [None, None]
+        self._ids_event = [None, None]
+        self._ids_turn = 0
 
     def sampler_h2d_bytes(self) -> int:
         return self.sampler.h2d_bytes_last
@@ -94,10 +123,60 @@ class LLM:
 
         While the GPU runs a step of single decode tokens, the next step is prepared as far as
         it does not depend on the tokens being sampled: the scheduler's decision, the pages and
-        the batch descriptor (`Scheduler.continue_decoding`, `Engine.prebuild`).  When the tokens
-        are there, only their ids are copied in.  If a request ends on its token, or a new one
-        has arrived, the preparation is given back and the step is scheduled the usual way.
+        the batch descriptor (`Scheduler.continue_decoding`, `Engine.prebuild`).  Where the
+        sampler needs nothing else of those tokens (no repetition penalty), the next step is
+        also launched, with the sampled ids copied into its descriptor on the device, before the
+        host reads them: the GPU does not wait for the host between decode steps.  Such a step is
+        never taken back.  If a request ends on a token that the host sees only afterwards (end
+        of sequence), its row of the step that ran ahead is dropped; a request that arrived
+        meanwhile is admitted one step later.  Where the next step cannot be launched, its
+        preparation is kept for the next call and given back if the state has changed by then.
         """
+        cur, self._ahead = self._ahead, None
+        if cur is not None:
+            live = [k for k, item in enumerate(cur.batch.items)
+                    if item.request.status is not RequestStatus.FINISHED]
+            if not live:
+                cur = None                   # every request of the step that ran ahead has ended
+            elif len(live) < len(cur.batch.items):
+                cur = _Launched(ScheduledBatch([cur.batch.items[k] for k in live], [], []),
+                                [cur.samplers[k] for k in live], cur.ids, cur.host, cur.event,
+                                live, False)
+        if cur is None:
+            cur = self._launch_next()
+            if cur is None:
+                return []
+        batch, samplers = cur.batch, cur.samplers
+        # the GPU is busy with the step: the host's part of the next one
+        self.scheduler.advance(batch)
+        if self.prepare_early and cur.whole and len(samplers) == len(batch.items):
+            nxt = self.scheduler.continue_decoding()
+            if nxt is not None:
+                prepared = self.engine.prebuild(
+                    [StepEntry(item.request.request_id, [0], [0]) for item in nxt.items])
+                if (self.run_ahead and cur.ids is not None
+                        and all(r.sampling_params.repetition_penalty == 1.0 for r in samplers)
+                        and len(nxt.items) == len(samplers)
+                        and all(i.request is r for i, r in zip(nxt.items, samplers))):
+                    logits = self.engine.run_prebuilt_fed(prepared, cur.ids, keep=False)
+                    # the token that is still on its way counts for the sampler's counters
+                    self._ahead = self._sample(nxt, samplers, logits, pending=1)
+                else:
+                    self._early = (nxt, prepared)
+        sampled: dict[int, int] = {}
+        if cur.ids is not None:
+            cur.event.synchronize()
+            host = cur.host.tolist()
+            self.d2h_bytes_last = 4 * len(host)
+            sampled = {r.request_id: int(host[k]) for r, k in zip(samplers, cur.rows)}
+        self.steps_run += 1
+        if self.steps_run % 256 == 0 and hasattr(self.engine.ops, "check_errors"):
+            self.engine.ops.check_errors()
+        return self.scheduler.update(batch, sampled, advanced=True)
+
+    def _launch_next(self) -> "_Launched | None":
+        """Schedule and launch a step (or launch the one prepared by the call before, if the
+        state is still the one it was prepared for)."""
         early, self._early = self._early, None
         if early is not None and not (self.scheduler.still_valid(early[0])
                                       and self.engine.prebuilt_is_current(early[1])):
@@ -114,7 +193,7 @@ class LLM:
                 if self.scheduler.has_unfinished() and not batch.preempted:
                     raise RuntimeError("nothing can be scheduled: the cache is too small for the "
                                        "request at the head of the queue")
-                return []
+                return None
             entries = []
             samplers = []
             for item in batch.items:
@@ -124,30 +203,32 @@ class LLM:
                 if item.samples:
                     samplers.append(item.request)
             logits = self.engine.run_reserved(entries, keep=False)     # sampled from at once
-        sampled: dict[int, int] = {}
-        ids = None
-        if samplers:
-            ids = self.sampler.sample(
-                logits, [r.sampling_params for r in samplers],
-                [len(r.output_tokens) for r in samplers], [r.seed for r in samplers],
-                [r.all_tokens if r.sampling_params.repetition_penalty != 1.0 else ()
-                 for r in samplers])
-        # the GPU is busy with the step: the host's part of the next one
-        self.scheduler.advance(batch)
-        if self.prepare_early and len(samplers) == len(batch.items):
-            nxt = self.scheduler.continue_decoding()
-            if nxt is not None:
-                prepared = self.engine.prebuild(
-                    [StepEntry(item.request.request_id, [0], [0]) for item in nxt.items])
-                self._early = (nxt, prepared)
-        if ids is not None:
-            host = ids.cpu()
-            self.d2h_bytes_last = host.numel() * host.element_size()
-            sampled = {r.request_id: int(t) for r, t in zip(samplers, host.tolist())}
-        self.steps_run += 1
-        if self.steps_run % 256 == 0 and hasattr(self.engine.ops, "check_errors"):
-            self.engine.ops.check_errors()
-        return self.scheduler.update(batch, sampled, advanced=True)
+        return self._sample(batch, samplers, logits, pending=0)
+
+    def _sample(self, batch: ScheduledBatch, samplers: list[Request], logits: torch.Tensor,
+                pending: int) -> "_Launched":
+        """Launch the sampler on the step's logits and the copy of its ids to the host, into one
+        of two pinned buffers in turn (the one of the step before may not have been read yet)."""
+        if not samplers:
+            return _Launched(batch, samplers, None, None, None, [], True)
+        ids = self.sampler.sample(
+            logits, [r.sampling_params for r in samplers],
+            [len(r.output_tokens) + pending for r in samplers], [r.seed for r in samplers],
+            [r.all_tokens if r.sampling_params.repetition_penalty != 1.0 else ()
+             for r in samplers])
+        n = len(samplers)
+        self._ids_turn ^= 1
+        turn = self._ids_turn
+        if self._ids_host[turn] is None or self._ids_host[turn].numel() < n:
+            self._ids_host[turn] = torch.empty(max(n, 64), dtype=torch.int32,
+                                               pin_memory=self.device.type == "cuda")
+            self._ids_event[turn] = (torch.cuda.Event() if self.device.type == "cuda"
+                                     else _NoEvent())
+        host = self._ids_host[turn][:n]
+        host.copy_(ids, non_blocking=True)
+        event = self._ids_event[turn]
+        event.record()
+        return _Launched(batch, samplers, ids, host, event, list(range(n)), True)
 
     def run(self, requests: Sequence[tuple[int, Request]]) -> list[Request]:
         """Run until all `(arrival_step, request)` pairs are finished

@@ -63,17 +63,40 @@ def test_end_of_sequence_arrives_while_the_next_step_is_prepared(root):
     want = []
     for o in free_run:
         want.append(o[:o.index(eos) + 1] if eos in o else o)
-    for early in (True, False):
+    for early, ahead in ((True, True), (True, False), (False, False)):
         llm = LLM(d, num_blocks=64, block_size=8, max_concurrent=4, dtype="float32", chunk_size=16,
                   eos_token_id=eos)
-        llm.prepare_early = early
+        llm.prepare_early, llm.run_ahead = early, ahead
         outs = llm.generate_many(prompts, max_new_tokens=24,
                                  sampling_params=SamplingParams(temperature=0.0))
-        assert outs == want, f"prepare_early={early}"
+        assert outs == want, f"prepare_early={early} run_ahead={ahead}"
         assert any(len(o) < 24 for o in outs)
         llm.step()                           # gives back what was prepared for a step that never came
         assert llm.engine.cache.free_pages() == [64] * len(llm.engine.cache.groups)
         llm.engine.cache.check_consistency()
+
+
+def test_steps_launched_ahead_sample_the_same_tokens(root):
+    """A decode step that is launched before the host has read the ids of the step before takes
+    them on the device and counts the token on its way for the random numbers: temperature,
+    top-k and top-p sampling give the same tokens with and without it, also when requests arrive
+    late and when one of them has a repetition penalty (which keeps its steps from running ahead)."""
+    from somi_inference_b200 import LLM, SamplingParams
+    d = make_model("C", root, torch.float32, std=STD)
+    cfg, _ = plain.load_folder(d)
+    prompts = [random_tokens(n, cfg["vocab_size"], 400 + i) for i, n in enumerate([5, 21, 40, 9])]
+    for penalty in (1.0, 1.3):
+        sps = [SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=11 + i,
+                              repetition_penalty=penalty if i == 2 else 1.0) for i in range(4)]
+        outs = []
+        for ahead in (True, False):
+            llm = LLM(d, num_blocks=64, block_size=8, max_concurrent=4, dtype="float32", chunk_size=16)
+            llm.run_ahead = ahead
+            outs.append(llm.generate_many(prompts, max_new_tokens=20, sampling_params=sps,
+                                          arrival_steps=[0, 0, 3, 9], ignore_eos=True))
+            llm.engine.cache.check_consistency()
+            assert llm.engine.cache.free_pages() == [64] * len(llm.engine.cache.groups)
+        assert outs[0] == outs[1], f"penalty {penalty}"
 
 
 def test_a_step_of_another_caller_between_prepared_steps(root):
