@@ -89,6 +89,7 @@ class LLM:
         self._early = None             # (scheduled batch, its descriptor) prepared for the next step
         self.run_ahead = True          # launch the next decode step before the host has the ids
         self._ahead: _Launched | None = None       # the step that was launched ahead
+        self.rows_dropped = 0          # rows of steps launched ahead whose request had ended
         self._ids_host = [None, None]
         self._ids_event = [None, None]
         self._ids_turn = 0
@@ -136,6 +137,7 @@ class LLM:
         if cur is not None:
             live = [k for k, item in enumerate(cur.batch.items)
                     if item.request.status is not RequestStatus.FINISHED]
+            self.rows_dropped += len(cur.batch.items) - len(live)
             if not live:
                 cur = None                   # every request of the step that ran ahead has ended
             elif len(live) < len(cur.batch.items):

@@ -80,6 +80,41 @@ def test_generation_through_the_entry_point_matches_plain_greedy(root):
     assert llm.generate(prompts[1], max_new_tokens=4, temperature=0.0) == outs[1][:4]
 
 
+def test_end_of_sequence_under_steps_launched_ahead(root):
+    """Decode steps are launched before the host has read the ids of the step before.  A request
+    that ends on such a token has a row in the step that ran ahead: the row is dropped, the others
+    go on, a late arrival is admitted afterwards, and every page comes back, with and without
+    running ahead."""
+    d = make_model("B", root, torch.float32, std=0.08)
+    cfg, w = plain.load_folder(d)
+    prompts = [random_tokens(n, cfg["vocab_size"], 200 + i) for i, n in enumerate([7, 19, 33, 12])]
+    free_run = [plain.greedy(cfg, w, p, 16) for p in prompts]
+    eos = free_run[1][6]
+    want = [o[:o.index(eos) + 1] if eos in o else o for o in free_run]
+    assert any(len(o) < 16 for o in want)
+    for ahead in (True, False):
+        llm = LLM(d, num_blocks=40, block_size=8, max_concurrent=3, device="cpu", dtype="float32",
+                  ops=HostOps(), chunk_size=16, eos_token_id=eos)
+        llm.run_ahead = ahead
+        launched_ahead = 0
+        reqs = [llm.make_request(p, max_new_tokens=16, sampling_params=SamplingParams(temperature=0.0))
+                for p in prompts]
+        pending = [(0, reqs[0]), (0, reqs[1]), (2, reqs[2]), (11, reqs[3])]
+        step = 0
+        while pending or llm.scheduler.has_unfinished():
+            while pending and pending[0][0] <= step:
+                llm.scheduler.add_request(pending.pop(0)[1])
+            llm.step()
+            launched_ahead += llm._ahead is not None
+            llm.engine.cache.check_consistency()
+            step += 1
+        assert [r.output_tokens for r in reqs] == want, f"run_ahead={ahead}"
+        assert (launched_ahead > 0) == ahead
+        assert (llm.rows_dropped > 0) == ahead
+        llm.step()
+        assert llm.engine.cache.free_pages() == [40]
+
+
 def test_preempted_request_generates_the_same_tokens(root):
     d = make_model("A", root, torch.float32, std=0.08)
     prompts = [random_tokens(n, 256, 70 + i) for i, n in enumerate([30, 28, 26])]
