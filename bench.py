@@ -108,13 +108,14 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(s)}
 
 
-def build_engine(shape: str, layers: int, batches: list[int], extra_tokens: int):
+def build_engine(shape: str, layers: int, batches: list[int], extra_tokens: int,
+                 context: int = CONTEXT, prefill_tokens: int = PREFILL_TOKENS):
     import torch
 
     from somi_inference_b200.config import Qwen2Config
     from somi_inference_b200.engine import Engine
     from somi_inference_b200.parts import declared_tensors
-    raw = dict(SHAPES[shape], num_hidden_layers=layers, max_position_embeddings=MAX_CONTEXT,
+    raw = dict(SHAPES[shape], num_hidden_layers=layers, max_position_embeddings=max(MAX_CONTEXT, context + extra_tokens, prefill_tokens),
                architectures=["Qwen2ForCausalLM"], hidden_act="silu", use_sliding_window=False)
     cfg = Qwen2Config.from_dict(raw)
     gen = torch.Generator(device="cuda").manual_seed(0)
@@ -127,7 +128,7 @@ def build_engine(shape: str, layers: int, batches: list[int], extra_tokens: int)
             tensors[name] = t.to(torch.bfloat16)
             del t
     page = 16
-    most = max(batches) * (CONTEXT + extra_tokens) + PREFILL_TOKENS + 4 * page
+    most = max(batches) * (context + extra_tokens) + prefill_tokens + 4 * page
     eng = Engine.from_tensors(cfg, tensors, dtype="bfloat16", page_size=page, max_tokens=most,
                               max_requests=max(batches) + 1)
     return cfg, eng
@@ -202,7 +203,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--only", choices=["decode", "prefill"], default=None,
                     help="run only this phase and print its figures (for profiling runs)")
-    ap.add_argument("--context", type=int, default=CONTEXT, help="cached tokens per request")
+    ap.add_argument("--context", type=int, default=CONTEXT,
+                    help="cached tokens per request (with --only decode)")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="length of the timed prompt (with --only prefill)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -224,7 +228,13 @@ def main() -> int:
     layers = args.layers or FULL_LAYERS[args.shape]
     batches = [args.batch] if args.no_points else sorted({1, args.batch, 64})
     extra = 2 * (args.steps + args.warmup) + 8
-    cfg, eng = build_engine(args.shape, layers, batches, extra)
+    if args.only is None and (args.context != CONTEXT or args.prefill_tokens != PREFILL_TOKENS):
+        print("bench.py: --context and --prefill-tokens go with --only decode / --only prefill")
+        return 2
+    if args.only is not None:
+        batches = [args.batch]
+    n_prefill = args.prefill_tokens
+    cfg, eng = build_engine(args.shape, layers, batches, extra, args.context, n_prefill)
     sampler = Sampler(eng.ops, eng.device)
     sizes = model_bytes_and_flops(cfg, layers)
     pk, pk_kind = peaks()
@@ -240,7 +250,7 @@ def main() -> int:
 
     # ---- prefill of 2,048 tokens (one request, one step), timed over a few repetitions
     g = torch.Generator().manual_seed(3)
-    prompt = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
+    prompt = torch.randint(0, V, (n_prefill,), generator=g).tolist()
     pre_ms = []
     # the same layout every time: from its third run on the step is replayed from the CUDA graph
     # that the engine captured at the second
@@ -248,15 +258,15 @@ def main() -> int:
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        eng.step([StepEntry(("prefill", rep), prompt, [PREFILL_TOKENS - 1])])
+        eng.step([StepEntry(("prefill", rep), prompt, [n_prefill - 1])])
         e.record()
         torch.cuda.synchronize()
         eng.end(("prefill", rep))
         pre_ms.append(s.elapsed_time(e))
     prefill_ms = sorted(pre_ms[2:])[len(pre_ms[2:]) // 2]
-    prefill_flops = (2 * sizes["matmul_params"] * PREFILL_TOKENS + 2 * sizes["head_params"]
-                     + layers * sizes["attn_flops_per_layer"](PREFILL_TOKENS))
-    prefill = {"value": round(PREFILL_TOKENS / prefill_ms * 1e3, 1), "tokens": PREFILL_TOKENS,
+    prefill_flops = (2 * sizes["matmul_params"] * n_prefill + 2 * sizes["head_params"]
+                     + layers * sizes["attn_flops_per_layer"](n_prefill))
+    prefill = {"value": round(n_prefill / prefill_ms * 1e3, 1), "tokens": n_prefill,
                "ms": round(prefill_ms, 3),
                "frac": round(prefill_flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
     if args.only == "prefill":

@@ -12,6 +12,7 @@
 // of the sequence with an online softmax, re-reading keys and values for every query head of
 // a group (somi_inference/core/paged_attention_triton.py:29-150); formulas in
 // somi_inference/core/paged_attention.py:352-413.
+#include "attention_merge.cuh"
 #include "mma.cuh"
 
 namespace somi {
@@ -217,29 +218,6 @@ paged_decode_split_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
     }
 }
 
-// Merge of the per-chunk partial results: one CTA per (request, query head), HD threads.
-template <int HD>
-__global__ void __launch_bounds__(HD)
-paged_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                          int max_splits, const int* __restrict__ ctx_len, int row_base,
-                          int req_base, int nq, int window, __nv_bfloat16* __restrict__ out) {
-    const int i = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
-    pdl_launch_dependents();
-    pdl_wait();
-    const DecodeRange rg = decode_range(ctx_len[req_base + i], window);
-    if (rg.n_splits - rg.first_split == 1) return;       // written by the split kernel
-    const size_t base = (static_cast<size_t>(i) * nq + head) * max_splits;
-    float M = -INFINITY;
-    for (int s = rg.first_split; s < rg.n_splits; ++s) M = fmaxf(M, part_ml[2 * (base + s)]);
-    float acc = 0.f, L = 0.f;
-    for (int s = rg.first_split; s < rg.n_splits; ++s) {
-        const float f = exp2f(part_ml[2 * (base + s)] - M);
-        acc += f * part_o[(base + s) * HD + d];
-        L += f * part_ml[2 * (base + s) + 1];
-    }
-    out[static_cast<size_t>(row_base + i) * nq * HD + head * HD + d] = __float2bfloat16_rn(acc / L);
-}
-
 template <int HD>
 int launch_decode(const void* qkv, int row_stride, int row_base, int req_base, int n_decode,
                   const void* kcache, const void* vcache, const int* block_table, int bt_stride,
@@ -257,11 +235,8 @@ int launch_decode(const void* qkv, int row_stride, int row_base, int req_base, i
         part_o, part_ml, max_splits, static_cast<__nv_bfloat16*>(out));
     int rc = launch_status();
     if (rc != 0 || max_splits == 1) return rc;
-    dim3 mgrid(n_decode, nq);
-    launch_pdl(paged_decode_merge_kernel<HD>, dim3(mgrid), dim3(HD), 0, stream, 
-        part_o, part_ml, max_splits, ctx_len, row_base, req_base, nq, window,
-        static_cast<__nv_bfloat16*>(out));
-    return launch_status();
+    return launch_decode_merge<HD>(part_o, part_ml, max_splits, kDecChunk, ctx_len, row_base, req_base,
+                                   n_decode, nq, window, static_cast<__nv_bfloat16*>(out), stream);
 }
 
 }  // namespace somi

@@ -231,6 +231,11 @@ DECODE_CASES = [
     # long contexts: many chunks per request
     (14, 2, 64, 16, None, [3900, 100, 2300]),
     (4, 2, 128, 16, None, [5000, 3]),
+    # more than 32 chunks: the merge in which the warps share the chunks, also with a window
+    # (the first chunks are skipped) and at head size 32
+    (14, 2, 64, 16, None, [9000, 70, 4224, 4225]),
+    (6, 2, 64, 16, 6000, [9000, 6100, 5999, 12]),
+    (3, 3, 32, 64, None, [4500, 129]),
 ]
 
 
