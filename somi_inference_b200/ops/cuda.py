@@ -72,6 +72,8 @@ class CudaOps:
         self._device_index = torch.cuda.current_device()
         self._tensor_maps: dict = {}
         self.use_tma_decode = True
+        self.lib.somi_decode_ring_chunks.argtypes = [ctypes.c_int]
+        self.lib.somi_decode_ring_chunks.restype = None
         self.use_tma_prefill = True
         self._gemm_maps: dict = {}
         self.use_skinny_gemm = True
@@ -194,6 +196,12 @@ class CudaOps:
             entry = (raw, addr)
             self._tensor_maps[key] = entry
         return entry[1]
+
+    def set_decode_ring_chunks(self, chunks: int) -> None:
+        """Chunks of 128 keys that one CTA of the TMA decode kernel walks through: 0 lets the
+        launcher choose from the step's size (the default), 1 forces the one-chunk kernel,
+        2..8 the ring kernel with that many."""
+        self.lib.somi_decode_ring_chunks(int(chunks))
 
     def set_pdl(self, on: bool) -> None:
         """Programmatic dependent launch for all kernels of the library (on by default)."""

@@ -137,6 +137,36 @@ def test_preemption_on_the_gpu_gives_the_same_tokens(root):
     assert [r.output_tokens for r in reqs] == want
 
 
+@pytest.mark.parametrize("chunks", [2, 3])
+def test_decoding_with_several_chunks_per_cta(root, chunks):
+    """Steps with thousands of 128-key chunks run decode attention with CTAs that walk through
+    several chunks (keys and values in rings).  Tiny models never get there by themselves, so
+    the choice is forced: four requests of different lengths, one of them beyond the window of
+    the windowed layers, decoded together for 150 steps across chunk and page edges."""
+    from somi_inference_b200.engine import Engine, StepEntry
+    d = make_model("D", root, torch.bfloat16, std=STD)
+    cfg, w = plain.load_folder(d)
+    lens = [300, 150, 260, 33]
+    steps = 150
+    ids = [random_tokens(n + steps, cfg["vocab_size"], 500 + i) for i, n in enumerate(lens)]
+    ref = [plain.logits(cfg, w, x) for x in ids]
+    scale = max(r.abs().max().item() for r in ref)
+    eng = Engine(d, dtype="bfloat16", page_size=16, max_tokens=4 * 512)
+    eng.ops.set_decode_ring_chunks(chunks)
+    try:
+        for i, n in enumerate(lens):
+            eng.step([StepEntry(i, ids[i][:n], [])])
+        worst = 0.0
+        for t in range(steps):
+            got = eng.step([StepEntry(i, [ids[i][n + t]], [0]) for i, n in enumerate(lens)]).float().cpu()
+            for i, n in enumerate(lens):
+                worst = max(worst, (got[i] - ref[i][n + t]).abs().max().item())
+        eng.ops.check_errors()
+    finally:
+        eng.ops.set_decode_ring_chunks(0)
+    assert worst <= 4e-2 * scale, f"chunks per CTA {chunks}: {worst / scale:.3e} of the logits' scale"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(root, dtype):
     """A 3-token prompt followed by 300 single-token steps (pages fill and follow one another),

@@ -239,12 +239,18 @@ DECODE_CASES = [
 ]
 
 
-@pytest.mark.parametrize("tma", [True, False], ids=["tma", "cp_async"])
+@pytest.mark.parametrize("tma", [True, False, 2, 3, 8], ids=["tma", "cp_async", "ring2", "ring3", "ring8"])
 @pytest.mark.parametrize("case", DECODE_CASES, ids=[f"d{i}" for i in range(len(DECODE_CASES))])
 def test_split_kv_decode_attention(ops, case, tma):
     """Single-token requests around the 128-key chunk edges, with and without a window, beside
-    one prompt portion; bfloat16 goes through the split-KV kernel."""
+    one prompt portion; bfloat16 goes through the split-KV kernel: the one with a chunk per
+    CTA, and the one whose CTAs walk through 2, 3 or 8 chunks with keys and values in rings
+    (which a step chooses by itself only when it has thousands of chunks)."""
     nq, nkv, hd, ps, window, ctxs = case
+    ring = 0 if isinstance(tma, bool) else tma
+    tma = bool(tma)
+    if ring and not ops.lib.somi_decode_tma_supported(nq, nkv, hd, ps):
+        pytest.skip("the ring kernel is part of the TMA path")
     assert ops.decode_supported(nq, nkv, hd, torch.bfloat16)
     reqs = [(c, 1) for c in ctxs] + [(40, 9)]
     mgr, batch, qkv, view, _ = attention_case(ops, nq=nq, nkv=nkv, hd=hd, page_size=ps,
@@ -253,12 +259,14 @@ def test_split_kv_decode_attention(ops, case, tma):
     out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
     before = ops.launches
     ops.use_tma_decode = tma
+    ops.set_decode_ring_chunks(ring if ring else 1)
     try:
         ops.paged_attention(qkv, view.keys, view.values, batch, batch.groups[0], nq, nkv, hd,
                             hd ** -0.5, window, out, storage=view.storage)
         ops.check_errors()
     finally:
         ops.use_tma_decode = True
+        ops.set_decode_ring_chunks(0)
     assert ops.launches - before >= 2      # one kernel for the portion, the split kernel for the rest
     ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
     cb = batch_to_cpu(batch)
