@@ -15,6 +15,8 @@ namespace somi {
 constexpr int kMergeWideFrom = 33;     // chunks per request from which the warps share them
 constexpr int kMergeWarps = 8;
 
+namespace {      // every file that includes this has kernels of its own (no symbol is shared)
+
 struct MergeRange {
     int first_split, n_splits;
 };
@@ -27,15 +29,17 @@ __device__ __forceinline__ MergeRange merge_range(int ctx_len, int window, int c
     return r;
 }
 
-template <int HD>
+// CHUNK: the keys per partial result, known at compile time here: the range is found with
+// shifts (a division by a run-time value at the head of this short kernel cost 1 µs).
+template <int HD, int CHUNK>
 __global__ void __launch_bounds__(HD)
 decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                    int max_splits, int chunk, const int* __restrict__ ctx_len, int row_base,
+                    int max_splits, const int* __restrict__ ctx_len, int row_base,
                     int req_base, int nq, int window, __nv_bfloat16* __restrict__ out) {
     const int i = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    const MergeRange rg = merge_range(ctx_len[req_base + i], window, chunk);
+    const MergeRange rg = merge_range(ctx_len[req_base + i], window, CHUNK);
     if (rg.n_splits - rg.first_split == 1) return;       // written by the split kernel
     const size_t base = (static_cast<size_t>(i) * nq + head) * max_splits;
     float M = -INFINITY;
@@ -106,18 +110,20 @@ decode_merge_wide_kernel(const float* __restrict__ part_o, const float* __restri
     }
 }
 
+}  // namespace
+
 // Launch the merge for `n_decode` requests (none if every request has a single chunk).
 template <int HD>
-int launch_decode_merge(const float* part_o, const float* part_ml, int max_splits, int chunk,
+static int launch_decode_merge(const float* part_o, const float* part_ml, int max_splits, int chunk,
                         const int* ctx_len, int row_base, int req_base, int n_decode, int nq,
                         int window, __nv_bfloat16* out, cudaStream_t stream) {
     dim3 grid(n_decode, nq);
-    if (max_splits >= kMergeWideFrom)
+    if (max_splits >= kMergeWideFrom || chunk != 128)
         launch_pdl(decode_merge_wide_kernel<HD>, grid, dim3(kMergeWarps * 32), 0, stream, part_o,
                    part_ml, max_splits, chunk, ctx_len, row_base, req_base, nq, window, out);
     else
-        launch_pdl(decode_merge_kernel<HD>, grid, dim3(HD), 0, stream, part_o, part_ml, max_splits,
-                   chunk, ctx_len, row_base, req_base, nq, window, out);
+        launch_pdl(decode_merge_kernel<HD, 128>, grid, dim3(HD), 0, stream, part_o, part_ml,
+                   max_splits, ctx_len, row_base, req_base, nq, window, out);
     return launch_status();
 }
 
