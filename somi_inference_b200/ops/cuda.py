@@ -256,52 +256,43 @@ class CudaOps:
         tensor_core_prefill = (batch.num_prefill_requests > 0
                                and self.prefill_supported(nq, nkv, hd, qkv.dtype))
         if tensor_core_prefill:
-            tiles = batch.tiles[self.prefill_q_tile]
-            tma = (self.use_tma_prefill and storage is not None and bool(
-                self.lib.somi_prefill_tma_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
-                                                    ctypes.c_int(hd), ctypes.c_int(page_size))))
-            # measured on 2,048-token prompts: the tcgen05 kernel is ahead at both of its head
-            # sizes (74 vs 160 us per 7B-shaped layer, 44 vs 67 us per 0.5B-shaped layer)
-            tc = (self.use_tc_prefill
-                  and storage is not None and qkv.shape[1] % 8 == 0 and bool(
-                self.lib.somi_prefill_tc_supported(ctypes.c_int(nq), ctypes.c_int(nkv),
-                                                   ctypes.c_int(hd), ctypes.c_int(page_size))))
-            if tc:
-                # both products on tcgen05 tensor cores, accumulators in tensor memory
+            # Three kernels, the first that takes the sizes: both products on tcgen05 with
+            # accumulators in tensor memory (measured on 2,048-token prompts: 60 vs 160 us per
+            # 7B-shaped layer, 25 vs 67 us per 0.5B-shaped layer), mma.sync fed by TMA, mma.sync
+            # fed by cp.async gathers.
+            sizes = (ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size))
+            row_bytes = hd * 2
+            if (self.use_tc_prefill and storage is not None and qkv.shape[1] % 8 == 0
+                    and bool(self.lib.somi_prefill_tc_supported(*sizes))):
                 tiles = batch.tiles[self.prefill_tc_q_tile]
-                row_bytes = hd * 2
                 rc = self.lib.somi_paged_attention_prefill_tc(
                     ctypes.c_void_p(self._q_tensor_map(qkv)),
                     ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)),
                     ctypes.c_longlong((kcache.data_ptr() - storage.data_ptr()) // row_bytes),
                     ctypes.c_longlong((vcache.data_ptr() - storage.data_ptr()) // row_bytes),
                     _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
-                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
-                    ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
                     ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
                 self._done(rc, "paged_attention_prefill_tc")
-                tma = None
-            if tma is None:
-                pass
-            elif tma:
-                row_bytes = hd * 2
+            elif (self.use_tma_prefill and storage is not None
+                  and bool(self.lib.somi_prefill_tma_supported(*sizes))):
+                tiles = batch.tiles[self.prefill_q_tile]
                 rc = self.lib.somi_paged_attention_prefill_tma(
                     ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)), _ptr(qkv),
                     ctypes.c_int(qkv.shape[1]),
                     ctypes.c_longlong((kcache.data_ptr() - storage.data_ptr()) // row_bytes),
                     ctypes.c_longlong((vcache.data_ptr() - storage.data_ptr()) // row_bytes),
                     _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
-                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
-                    ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
                     ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
+                self._done(rc, "paged_attention_prefill_tma")
             else:
+                tiles = batch.tiles[self.prefill_q_tile]
                 rc = self.lib.somi_paged_attention_prefill(
                     _ptr(qkv), ctypes.c_int(qkv.shape[1]), _ptr(kcache), _ptr(vcache),
                     _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
-                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]),
-                    ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
                     ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
-            if tma is not None:
                 self._done(rc, "paged_attention_prefill")
         tiles = batch.tiles[self.generic_q_tile]
         n_generic_tiles = 0 if tensor_core_prefill else tiles.shape[0]

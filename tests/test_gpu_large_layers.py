@@ -25,7 +25,7 @@ SHAPES = {
 def weights(request):
     from somi_inference_b200.config import Qwen2Config
     from somi_inference_b200.parts import declared_tensors
-    raw = dict(SHAPES[request.param], num_hidden_layers=2, max_position_embeddings=1024,
+    raw = dict(SHAPES[request.param], num_hidden_layers=2, max_position_embeddings=4608,
                architectures=["Qwen2ForCausalLM"], hidden_act="silu", use_sliding_window=False)
     cfg = Qwen2Config.from_dict(raw)
     gen = torch.Generator(device="cuda").manual_seed(0)
@@ -64,4 +64,35 @@ def test_bfloat16_against_float32_at_large_layer_sizes(weights, batch):
     scale = ref.abs().max().item()
     rms = ((got - ref) ** 2).mean().sqrt().item()
     assert rms <= 4e-3 * scale, f"{name} batch {batch}: rms {rms / scale:.2e} of the largest logit"
+    assert (got - ref).abs().max().item() <= 4e-2 * scale
+
+
+def test_bfloat16_against_float32_with_thousands_of_chunks(weights):
+    """A decode step with more than 16 chunks of 128 keys per SM takes the attention kernel whose
+    CTAs walk through several chunks, and a merge over fewer, larger partial results: many
+    requests with contexts of a few thousand tokens, of different lengths."""
+    from somi_inference_b200.engine import Engine, StepEntry
+    name, cfg, tensors = weights
+    batch, ctx = {"7b": (40, 2100), "0.5b": (48, 4200)}[name]
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    assert -(-ctx // 128) * cfg.num_key_value_heads * batch >= 16 * sms, "the step is meant to be large"
+    g = torch.Generator().manual_seed(7)
+    lens = [ctx - 37 * (i % 7) for i in range(batch)]
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    feed = torch.randint(0, cfg.vocab_size, (4, batch), generator=g).tolist()
+    outs = []
+    for dtype in ("bfloat16", "float32"):
+        tt = tensors if dtype == "bfloat16" else {k: v.float() for k, v in tensors.items()}
+        eng = Engine.from_tensors(cfg, tt, dtype=dtype, page_size=16, max_tokens=sum(lens) + 64 * batch,
+                                  max_requests=batch)
+        for i, p in enumerate(prompts):
+            eng.step([StepEntry(i, p, [])])
+        res = [eng.step([StepEntry(i, [feed[s][i]], [0]) for i in range(batch)]) for s in range(4)]
+        eng.ops.check_errors()
+        outs.append(torch.cat([r.float() for r in res]))
+        del eng, tt
+    got, ref = outs
+    scale = ref.abs().max().item()
+    rms = ((got - ref) ** 2).mean().sqrt().item()
+    assert rms <= 4e-3 * scale, f"{name}: rms {rms / scale:.2e} of the largest logit"
     assert (got - ref).abs().max().item() <= 4e-2 * scale
