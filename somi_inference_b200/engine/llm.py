@@ -232,6 +232,12 @@ class LLM:
         event.record()
         return _Launched(batch, samplers, ids, host, event, list(range(n)), True)
 
+    def abort(self, request: Request) -> bool:
+        """Stop a request between two steps; its pages go back at once.  A decode step that was
+        launched ahead with a row for it drops that row; one that was only prepared is given
+        back and scheduled again.  Returns whether the request was still unfinished."""
+        return self.scheduler.abort(request)
+
     def run(self, requests: Sequence[tuple[int, Request]]) -> list[Request]:
         """Run until all `(arrival_step, request)` pairs are finished
         (somi_inference/core/continuous_batching.py:179-205)."""
@@ -285,9 +291,14 @@ class LLM:
         req = self.make_request(list(prompt), max_new_tokens=max_new_tokens, sampling_params=sp)
         self.scheduler.add_request(req)
         sent = 0
-        while self.scheduler.has_unfinished():
-            self.step()
-            self.scheduler.drain_finished()
-            while sent < len(req.output_tokens):
-                yield req.output_tokens[sent]
-                sent += 1
+        try:
+            while self.scheduler.has_unfinished():
+                self.step()
+                self.scheduler.drain_finished()
+                while sent < len(req.output_tokens):
+                    yield req.output_tokens[sent]
+                    sent += 1
+        finally:
+            # a reader that stops early leaves nothing behind
+            if self.abort(req):
+                self.scheduler.drain_finished()

@@ -135,6 +135,27 @@ class Scheduler:
         req.status = RequestStatus.WAITING
         self.waiting.append(req)
 
+    def abort(self, req: Request) -> bool:
+        """Take a request out, whatever its state: what it holds in the cache (reserved pages of a
+        step that is prepared or on its way included) goes back at once.  Returns whether it was
+        still unfinished.  (The reference has no such call; a caller that stops reading a stream
+        needs it.)"""
+        if req.status is RequestStatus.FINISHED:
+            return False
+        if req in self.running:
+            self.running.remove(req)
+        else:
+            try:
+                self.waiting.remove(req)
+            except ValueError:
+                return False                      # never added
+        if self.cache.is_registered(req.request_id):
+            self.cache.release(req.request_id)
+        req.status = RequestStatus.FINISHED
+        req.finish_reason = "aborted"
+        self.finished.append(req)
+        return True
+
     def has_unfinished(self) -> bool:
         return bool(self.waiting) or bool(self.running)
 

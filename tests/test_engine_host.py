@@ -155,3 +155,48 @@ def test_toy_architecture_is_registered_built_and_stepped(root):
     finally:
         unregister_architecture(toy_model.ARCH)
         unregister_toys()
+
+
+def test_abort_and_a_stream_that_is_closed_early(root):
+    """A request that is aborted between steps leaves the others' tokens unchanged, also when a
+    decode step with a row for it is on its way; a stream whose reader stops leaves no request
+    and no page behind."""
+    d = make_model("B", root, torch.float32, std=0.08)
+    cfg, w = plain.load_folder(d)
+    prompts = [random_tokens(n, cfg["vocab_size"], 600 + i) for i, n in enumerate([9, 17, 5])]
+    want = [plain.greedy(cfg, w, p, 12) for p in prompts]
+    for ahead in (True, False):
+        llm = LLM(d, num_blocks=40, block_size=8, max_concurrent=3, device="cpu", dtype="float32",
+                  ops=HostOps(), chunk_size=16)
+        llm.run_ahead = ahead
+        reqs = [llm.make_request(p, max_new_tokens=12, sampling_params=SamplingParams(temperature=0.0),
+                                 ignore_eos=True) for p in prompts]
+        for r in reqs:
+            llm.scheduler.add_request(r)
+        steps = 0
+        while llm.scheduler.has_unfinished():
+            llm.step()
+            steps += 1
+            if steps == 5:
+                assert (llm._ahead is not None) == ahead
+                assert llm.abort(reqs[1])
+            llm.engine.cache.check_consistency()
+        assert reqs[0].output_tokens == want[0] and reqs[2].output_tokens == want[2]
+        assert reqs[1].finish_reason == "aborted" and reqs[1].output_tokens == want[1][:len(reqs[1].output_tokens)]
+        assert 0 < len(reqs[1].output_tokens) < 12
+        llm.step()
+        assert llm.engine.cache.free_pages() == [40]
+        # a stream read for three tokens only
+        llm.scheduler.drain_finished()
+        got = []
+        stream = llm.generate_stream(prompts[0], max_new_tokens=12, temperature=0.0)
+        for t in stream:
+            got.append(t)
+            if len(got) == 3:
+                break
+        stream.close()
+        assert got == want[0][:3]
+        assert not llm.scheduler.has_unfinished()
+        llm.step()
+        assert llm.engine.cache.free_pages() == [40]
+        assert llm.generate(prompts[2], max_new_tokens=12, temperature=0.0, ignore_eos=True) == want[2]

@@ -249,3 +249,32 @@ def test_no_early_decision_when_it_would_depend_on_the_token():
     s2.advance(b)
     assert s2.continue_decoding() is None and cache2.free_pages() == [0]
     cache2.check_consistency()
+
+
+def test_abort_gives_everything_back_whatever_the_state():
+    cache, s = make(num_pages=8, page_size=4, max_concurrent=2)
+    a, b, c = req(0, 6, max_new=8), req(1, 5, max_new=8), req(2, 3, max_new=8)
+    for r in (a, b, c):
+        s.add_request(r)
+    run_step(s)                                          # a and b run, c waits
+    assert [r.request_id for r in s.running] == [0, 1] and list(s.waiting) == [c]
+    assert s.abort(c) and c.status is RequestStatus.FINISHED and c.finish_reason == "aborted"
+    assert not s.waiting
+    # b is aborted while the next decode step is decided and its page reserved
+    run_step(s)
+    nxt = s.schedule()
+    s.advance(nxt)
+    early = s.continue_decoding()
+    assert early is not None and len(early.items) == 2
+    s.update(nxt, {0: 9, 1: 9}, advanced=True)
+    assert s.abort(b)
+    assert not s.still_valid(early)
+    s.abandon(early)
+    cache.check_consistency()
+    assert [r.request_id for r in s.running] == [0]
+    assert not s.abort(b)                                 # already out
+    assert not s.abort(req(7, 3))                         # never added
+    while s.has_unfinished():
+        run_step(s)
+    assert cache.free_pages() == [8]
+    assert {r.request_id for r in s.drain_finished()} == {0, 1, 2}
