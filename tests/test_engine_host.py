@@ -200,3 +200,53 @@ def test_abort_and_a_stream_that_is_closed_early(root):
         llm.step()
         assert llm.engine.cache.free_pages() == [40]
         assert llm.generate(prompts[2], max_new_tokens=12, temperature=0.0, ignore_eos=True) == want[2]
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_schedules_with_ends_aborts_and_late_arrivals(root, seed):
+    """Random prompts, arrival steps, token budgets, pool sizes and policies; an end-of-sequence
+    token that some requests meet, and one request aborted on the way.  Every other request must
+    give plain greedy decoding's tokens (cut at the end-of-sequence token), and the cache must be
+    consistent after every step and empty at the end."""
+    import random
+    rng = random.Random(1000 + seed)
+    name = rng.choice(["A", "B"])
+    d = make_model(name, root, torch.float32, std=0.08)
+    cfg, w = plain.load_folder(d)
+    n = rng.randrange(2, 6)
+    new = rng.choice([3, 8, 14])
+    limit = cfg["max_position_embeddings"] - new - 1
+    prompts = [random_tokens(rng.randrange(1, min(limit, 60)), cfg["vocab_size"], 50 * seed + i)
+               for i in range(n)]
+    free_run = [plain.greedy(cfg, w, p, new) for p in prompts]
+    eos = rng.choice(rng.choice(free_run))               # a token that does come up
+    want = [o[:o.index(eos) + 1] if eos in o else o for o in free_run]
+    page = rng.choice([4, 8, 16])
+    need = max(-(-(len(p) + new) // page) for p in prompts)
+    llm = LLM(d, num_blocks=rng.choice([need + 1, 2 * need, 64]), block_size=page,
+              max_concurrent=rng.choice([1, 2, 4]), device="cpu", dtype="float32", ops=HostOps(),
+              chunk_size=rng.choice([2, 7, 16, 64]), max_num_batched_tokens=rng.choice([8, 24, 64]),
+              policy=rng.choice(["preempt", "reserve"]), eos_token_id=eos)
+    llm.run_ahead = rng.random() < 0.7
+    reqs = [llm.make_request(p, max_new_tokens=new, sampling_params=SamplingParams(temperature=0.0))
+            for p in prompts]
+    pending = sorted(((rng.randrange(0, 8), i) for i in range(n)))
+    victim, abort_at = rng.randrange(n), rng.randrange(1, 12)
+    step = 0
+    while pending or llm.scheduler.has_unfinished():
+        while pending and pending[0][0] <= step:
+            llm.scheduler.add_request(reqs[pending.pop(0)[1]])
+        llm.step()
+        step += 1
+        if step == abort_at:
+            llm.abort(reqs[victim])
+        llm.engine.cache.check_consistency()
+        assert step < 2000
+    llm.step()
+    pools = len(llm.engine.cache.groups)
+    assert llm.engine.cache.free_pages() == [llm.engine.num_pages] * pools
+    for i, r in enumerate(reqs):
+        if r.finish_reason == "aborted":
+            assert i == victim and r.output_tokens == want[i][:len(r.output_tokens)]
+        else:
+            assert r.output_tokens == want[i], f"request {i}"
