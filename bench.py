@@ -301,16 +301,19 @@ def main() -> int:
         llm.step()
     torch.cuda.synchronize()
     n0 = sum(len(r.output_tokens) for r in e2e_reqs)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        llm.step()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+    with ClockSampler() as e2e_clocks:
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            llm.step()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
     n1 = sum(len(r.output_tokens) for r in e2e_reqs)
     e2e = {"value": round((n1 - n0) / dt, 1), "unit": "tokens/s",
            "h2d_bytes_per_step": int(llm.engine.builder.h2d_bytes_last + llm.sampler_h2d_bytes()
                                      + llm.engine.token_patch_bytes),
-           "d2h_bytes_per_step": int(llm.d2h_bytes_last), "ms_per_step": round(dt / args.steps * 1e3, 3)}
+           "d2h_bytes_per_step": int(llm.d2h_bytes_last), "ms_per_step": round(dt / args.steps * 1e3, 3),
+           # this region runs later than the device-timed one, under the power cap often at a lower clock
+           "sm_mhz": e2e_clocks.summary().get("sm_mhz")}
     for r in e2e_reqs:
         if llm.engine.has(r.request_id):
             llm.engine.end(r.request_id)
