@@ -11,7 +11,9 @@ head-of-line blocking, the finish rule (EOS or max_new_tokens, EOS kept in the
 output: :150-158) and `max_concurrent`, and adds:
 
 * a token budget per step and prompt portions of at most `chunk_size` tokens,
-  scheduled beside the single decode tokens of running requests;
+  scheduled beside the single decode tokens of running requests; the decode tokens are
+  served first (no running request that decodes waits for another one's prompt), portions
+  share what is left of the budget;
 * pages are taken per step for exactly the scheduled tokens.  Policy "preempt"
   (default): when a running request cannot get a page, the most recently
   admitted running request is preempted by recompute: its pages go back, it
@@ -119,19 +121,32 @@ class Scheduler:
     def _pages_for(self, n_tokens: int) -> int:
         return -(-n_tokens // self.cache.page_size)
 
-    def _worst_case_pages(self, req: Request) -> int:
-        """ceil((prompt + max_new - 1) / page_size), as continuous_batching.py:64-67."""
-        return self._pages_for(len(req.prompt_tokens) + req.max_new_tokens - 1)
+    def _worst_case_pages(self, req: Request) -> list[int]:
+        """For every group of the cache, the most pages the request can hold at a time.  A group
+        that keeps all keys: ceil((prompt + max_new - 1) / page_size), as
+        continuous_batching.py:64-67.  A group with a window of w keeps the pages between the
+        oldest key a query still reads and the end of the portion being written: at most
+        ceil((w + portion) / page_size) + 1, whatever the length."""
+        full = self._pages_for(len(req.prompt_tokens) + req.max_new_tokens - 1)
+        out = []
+        for g in self.cache.groups:
+            w = g.needs.window
+            if w is None:
+                out.append(full)
+            else:
+                out.append(min(full, self._pages_for(w + self.chunk_size) + 1))
+        return out
 
     def add_request(self, req: Request) -> None:
         most = len(req.prompt_tokens) + req.max_new_tokens - 1
         if most > self.max_positions:
             raise ValueError(f"request {req.request_id}: prompt + max_new_tokens - 1 = {most} "
                              f"exceeds the model's {self.max_positions} positions")
-        pool = min(g.pool.num_pages for g in self.cache.groups) if self.cache.groups else None
-        if pool is not None and self._worst_case_pages(req) > pool:
-            raise ValueError(f"request {req.request_id} needs {self._worst_case_pages(req)} pages "
-                             f"at its longest; the cache has {pool}")
+        for g, need in zip(self.cache.groups, self._worst_case_pages(req)):
+            if need > g.pool.num_pages:
+                raise ValueError(f"request {req.request_id} needs {need} pages at its longest; "
+                                 f"the cache has {g.pool.num_pages}"
+                                 + (f" (window {g.needs.window})" if g.needs.window else ""))
         req.status = RequestStatus.WAITING
         self.waiting.append(req)
 
@@ -165,15 +180,18 @@ class Scheduler:
 
     # --------------------------------------------------------------- schedule
     def _preempt(self, victim: Request, items: list[ScheduledItem],
-                 preempted: list[Request]) -> None:
+                 preempted: list[Request]) -> int:
+        """Take `victim` out by recompute; returns the tokens of the step that it gives back."""
         self.cache.release(victim.request_id)
         self.running.remove(victim)
+        given_back = sum(i.num_tokens for i in items if i.request is victim)
         items[:] = [i for i in items if i.request is not victim]
         victim.status = RequestStatus.WAITING
         victim.num_computed = 0
         victim.num_preemptions += 1
         self.waiting.appendleft(victim)
         preempted.append(victim)
+        return given_back
 
     def schedule(self) -> ScheduledBatch:
         budget = self.max_num_batched_tokens
@@ -181,40 +199,57 @@ class Scheduler:
         preempted: list[Request] = []
         admitted: list[Request] = []
 
-        # 1. everything that is running continues: one decode token, or the next prompt portion
-        for req in list(self.running):
-            if req not in self.running:        # preempted while an earlier one was served
-                continue
-            if budget == 0:
-                break
-            left = req.num_tokens - req.num_computed
-            n = min(left, self.chunk_size, budget)
+        def serve(req: Request, n: int) -> int:
+            """Reserve `n` tokens for a running request, preempting from the back of the line
+            while pages are missing; returns the change of the budget."""
+            back = 0
             while True:
                 try:
                     self.cache.reserve(req.request_id, n)
                     break
                 except OutOfPages:
                     victim = self.running[-1]
-                    self._preempt(victim, items, preempted)
+                    back += self._preempt(victim, items, preempted)
                     if victim is req:
-                        n = 0
-                        break
-            if n == 0:
-                continue
+                        return back
             items.append(ScheduledItem(req, req.num_computed, n, req.num_computed + n == req.num_tokens))
-            budget -= n
+            return back - n
+
+        # 1. every running request that decodes gets its one token first, in admission order
+        #    (continuous_batching.py:91 decodes every running sequence in every step) ...
+        for req in list(self.running):
+            if budget <= 0:
+                break
+            if req in self.running and req.num_tokens - req.num_computed == 1:
+                budget += serve(req, 1)
+        # ... then the requests that are still in their prompt (or recomputing after a
+        # preemption) share what is left, in portions
+        for req in list(self.running):
+            if budget <= 0:
+                break
+            left = req.num_tokens - req.num_computed
+            if req in self.running and left > 1 and not any(i.request is req for i in items):
+                budget += serve(req, min(left, self.chunk_size, budget))
 
         # 2. admission, first come first served, head of the line blocks
-        reserved_worst = sum(self._worst_case_pages(r) for r in self.running)
+        reserved_worst = [0] * len(self.cache.groups)
+        if self.policy == "reserve":
+            for r in self.running:
+                reserved_worst = [a + b for a, b in zip(reserved_worst, self._worst_case_pages(r))]
         while (self.waiting and len(self.running) < self.max_concurrent and budget > 0
                and not preempted):
             req = self.waiting[0]
             n = min(req.num_tokens - req.num_computed, self.chunk_size, budget)
             if self.policy == "reserve":
-                pool = min(g.pool.num_pages for g in self.cache.groups)
-                if reserved_worst + self._worst_case_pages(req) > pool:
+                worst = self._worst_case_pages(req)
+                if any(a + b > g.pool.num_pages
+                       for a, b, g in zip(reserved_worst, worst, self.cache.groups)):
                     break
-            self.cache.register(req.request_id)
+                reserved_worst = [a + b for a, b in zip(reserved_worst, worst)]
+            try:
+                self.cache.register(req.request_id)
+            except OutOfPages:                 # every state slot of the cache is taken
+                break
             try:
                 self.cache.reserve(req.request_id, n)
             except OutOfPages:
@@ -224,7 +259,6 @@ class Scheduler:
             req.status = RequestStatus.RUNNING
             self.running.append(req)
             admitted.append(req)
-            reserved_worst += self._worst_case_pages(req)
             items.append(ScheduledItem(req, req.num_computed, n, req.num_computed + n == req.num_tokens))
             budget -= n
         return ScheduledBatch(items, preempted, admitted)

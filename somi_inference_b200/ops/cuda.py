@@ -9,10 +9,10 @@ compiled library, construction fails.
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 
+from . import trace
 from .build import build as _build_library
 
 _F32, _BF16 = 0, 1
@@ -80,10 +80,6 @@ class CudaOps:
         self.skinny_max_tokens = int(self.lib.somi_skinny_gemm_max_tokens())
         self._retired: list = []
         self.launches = 0     # kernels of this library launched so far
-        if os.environ.get("SOMI_B200_PDL", "1") == "0":
-            self.set_pdl(False)
-        if os.environ.get("SOMI_B200_SKINNY", "1") == "0":      # for A/B measurements
-            self.use_skinny_gemm = False
 
     # ------------------------------------------------------------------ util
     def _stream(self) -> ctypes.c_void_p:
@@ -114,6 +110,9 @@ class CudaOps:
                                  ctypes.c_int(ids.shape[0]), ctypes.c_int(table.shape[1]),
                                  self._stream())
         self._done(rc, "embed")
+        if trace.active():
+            n = ids.shape[0] * table.shape[1]
+            trace.note("embed", n * (table.element_size() + 4))
 
     def add_rmsnorm(self, residual, delta, weight, eps, out, rows=None) -> None:
         """residual += delta (float32, in place); out = rmsnorm(residual) * weight.
@@ -136,6 +135,14 @@ class CudaOps:
             ctypes.c_int(n_out), ctypes.c_int(H), ctypes.c_int(0 if rows is not None else 1),
             self._stream())
         self._done(rc, "add_rmsnorm")
+        if trace.active():
+            n = n_out * H
+            moved = n * (4 + out.element_size()) + H * weight.element_size()
+            if delta is not None:
+                moved += splits * n * delta.element_size()
+            if rows is None:
+                moved += n * 4
+            trace.note("add_rmsnorm", moved, detail=f"splits={splits}" if splits > 1 else "")
 
     def rope_store(self, qkv, positions, inv_freq, nq, nkv, hd, rotary_dim, slot_map, kcache,
                    vcache, partials=None, bias=None) -> None:
@@ -158,12 +165,18 @@ class CudaOps:
                 ctypes.c_int(hd), ctypes.c_int(rotary_dim), _ptr(slot_map), _ptr(kcache),
                 _ptr(vcache), ctypes.c_int(page_size), self._stream())
             self._done(rc, "rope_store_partial")
+            if trace.active():
+                n = qkv.shape[0] * qkv.shape[1]
+                trace.note("rope_store", partials.shape[0] * n * 4 + n * 2, detail="from partial sums")
             return
         rc = self.lib.somi_rope_store(
             _ptr(qkv), _code(qkv), _ptr(positions), _ptr(inv_freq), ctypes.c_int(qkv.shape[0]),
             ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(rotary_dim),
             _ptr(slot_map), _ptr(kcache), _ptr(vcache), ctypes.c_int(page_size), self._stream())
         self._done(rc, "rope_store")
+        if trace.active():
+            n = qkv.shape[0] * qkv.shape[1]
+            trace.note("rope_store", n * qkv.element_size() * 2)
 
     def _scratch(self, n_floats: int, device) -> torch.Tensor:
         """Float32 scratch that outlives the call (kernels of a captured graph keep its address)."""
@@ -239,6 +252,25 @@ class CudaOps:
             raise KernelError("the tcgen05 matrix product gave up waiting on a barrier; "
                               "its results are not valid")
 
+    @staticmethod
+    def _attention_work(batch, first: int, last: int, nq: int, nkv: int, hd: int, elt: int,
+                        window: int) -> tuple[float, float]:
+        """Bytes and flops of attention for requests [first, last) of the batch: every key and
+        value of a request's context once, queries in and outputs out; two products per
+        (query, key) pair that the mask leaves."""
+        moved = flops = 0.0
+        cu, ctx = batch.host.cu_q, batch.host.ctx_len
+        for r in range(first, last):
+            q, c = int(cu[r + 1] - cu[r]), int(ctx[r])
+            pairs = q * c + q * (q + 1) // 2
+            kv = c + q
+            if window:
+                pairs = sum(min(c + i + 1, window) for i in range(q)) if q < 4096 else min(pairs, q * window)
+                kv = min(kv, window + q - 1)
+            moved += 2 * kv * nkv * hd * elt + 2 * q * nq * hd * elt
+            flops += 4.0 * nq * hd * pairs
+        return moved, flops
+
     def paged_attention(self, qkv, kcache, vcache, batch, group, nq, nkv, hd, scale, window,
                         out, storage=None) -> None:
         """Attention of every token of the step over the cache (keys/values already stored).
@@ -274,6 +306,7 @@ class CudaOps:
                     _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
                     ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
                 self._done(rc, "paged_attention_prefill_tc")
+                kernel = "attention_prefill_tcgen05"
             elif (self.use_tma_prefill and storage is not None
                   and bool(self.lib.somi_prefill_tma_supported(*sizes))):
                 tiles = batch.tiles[self.prefill_q_tile]
@@ -286,6 +319,7 @@ class CudaOps:
                     _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
                     ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
                 self._done(rc, "paged_attention_prefill_tma")
+                kernel = "attention_prefill_tma"
             else:
                 tiles = batch.tiles[self.prefill_q_tile]
                 rc = self.lib.somi_paged_attention_prefill(
@@ -294,6 +328,10 @@ class CudaOps:
                     _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
                     ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
                 self._done(rc, "paged_attention_prefill")
+                kernel = "attention_prefill_cp_async"
+            if trace.active():
+                trace.note(kernel, *self._attention_work(batch, 0, batch.num_prefill_requests, nq,
+                                                         nkv, hd, qkv.element_size(), win))
         tiles = batch.tiles[self.generic_q_tile]
         n_generic_tiles = 0 if tensor_core_prefill else tiles.shape[0]
         n_generic_decode = 0 if split else n_decode
@@ -307,6 +345,11 @@ class CudaOps:
                 ctypes.c_int(hd), ctypes.c_int(page_size), ctypes.c_float(scale),
                 ctypes.c_int(win), _ptr(out), self._stream())
             self._done(rc, "paged_attention")
+            if trace.active():
+                first = batch.num_prefill_requests if tensor_core_prefill else 0
+                last = batch.num_prefill_requests if split else batch.num_requests
+                trace.note("attention_generic", *self._attention_work(
+                    batch, first, last, nq, nkv, hd, qkv.element_size(), win))
         if split:
             chunk = self.decode_chunk
             max_splits = -(-group.width * page_size // chunk)
@@ -342,6 +385,12 @@ class CudaOps:
             self._done(rc, "paged_attention_decode")
             if max_splits > 1:
                 self.launches += 1
+            if trace.active():
+                trace.note("attention_decode_tma" if tma else "attention_decode_cp_async",
+                           *self._attention_work(batch, batch.num_prefill_requests,
+                                                 batch.num_requests, nq, nkv, hd,
+                                                 qkv.element_size(), win),
+                           detail="with merge" if max_splits > 1 else "")
 
     def silu_mul(self, gu: torch.Tensor, out: torch.Tensor, interleaved: bool = False) -> None:
         """out = silu(gate) * up; gate/up are the two halves of `gu`'s rows, or alternate."""
@@ -350,6 +399,8 @@ class CudaOps:
                                     ctypes.c_int(out.shape[1]), ctypes.c_int(1 if interleaved else 0),
                                     self._stream())
         self._done(rc, "silu_mul")
+        if trace.active():
+            trace.note("silu_mul", (gu.numel() + out.numel()) * gu.element_size())
 
     # ------------------------------------------------------- tcgen05 matrix product
     GEMM_BF16, GEMM_F32, GEMM_PARTIAL_F32, GEMM_SWIGLU = 0, 1, 2, 3
@@ -423,6 +474,9 @@ class CudaOps:
             _code(bias) if bias is not None else _F32, _ptr(out),
             ctypes.c_int(1 if deep_ring else 0), self._stream())
         self._done(rc, "skinny_gemm")
+        if trace.active():
+            trace.note("skinny_gemm", (N * K + M * K) * 2 + out.numel() * out.element_size(),
+                       2.0 * M * N * K, detail=f"M={M} N={N} K={K} mode={mode}")
         return out
 
     def sample(self, logits, temperature, top_k, top_p, penalty, seed, counter, hist_off,
@@ -436,6 +490,8 @@ class CudaOps:
                                   _ptr(top_p), _ptr(penalty), _ptr(seed), _ptr(counter),
                                   _ptr(hist_off), _ptr(hist_tok), _ptr(out), self._stream())
         self._done(rc, "sample")
+        if trace.active():
+            trace.note("sample", logits.numel() * 4)
 
     def uniform(self, seed: int, counter: int) -> float:
         """The uniform number in [0, 1) that row (seed, counter) draws (host evaluation)."""

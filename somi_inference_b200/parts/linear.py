@@ -14,6 +14,8 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
+from ..ops import trace
+
 
 class Linear:
     def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None = None, ops=None) -> None:
@@ -30,7 +32,15 @@ class Linear:
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if self.skinny(x):
             return self.ops.skinny_gemm(x, self.weight, self.bias, self.ops.GEMM_BF16)
-        return F.linear(x, self.weight, self.bias)
+        y = F.linear(x, self.weight, self.bias)
+        self._note(x, y)
+        return y
+
+    def _note(self, x: torch.Tensor, y: torch.Tensor) -> None:
+        if trace.active():
+            M, N, K = x.shape[0], self.out_features, self.in_features
+            trace.note("library_gemm", (N * K + M * K) * x.element_size() + y.numel() * y.element_size(),
+                       2.0 * M * N * K, detail=f"M={M} N={N} K={K}")
 
     def partial_sums(self, x: torch.Tensor) -> torch.Tensor | None:
         """float32 [splits, M, out] partial sums over ranges of K (bias in the first), for a
@@ -50,11 +60,26 @@ class Linear:
 
     def to_float32(self, x: torch.Tensor) -> torch.Tensor:
         """x W^T with a float32 result (accumulation is float32 in every path)."""
-        if x.dtype == torch.float32:
-            return F.linear(x, self.weight)
         if self.skinny(x):
             return self.ops.skinny_gemm(x, self.weight, None, self.ops.GEMM_F32)
-        try:
-            return torch.mm(x, self.weight.t(), out_dtype=torch.float32)
-        except (TypeError, RuntimeError):
-            return F.linear(x, self.weight).float()
+        if x.dtype == torch.float32:
+            y = F.linear(x, self.weight)
+        elif _MM_TAKES_OUT_DTYPE:
+            y = torch.mm(x, self.weight.t(), out_dtype=torch.float32)
+        else:
+            y = F.linear(x, self.weight).float()      # rounds the logits to bfloat16 first
+        self._note(x, y)
+        return y
+
+
+def _mm_takes_out_dtype() -> bool:
+    """Whether this torch has `torch.mm(..., out_dtype=)` (asked once, without a device)."""
+    try:
+        torch.mm(torch.zeros(1, 1, device="meta", dtype=torch.bfloat16),
+                 torch.zeros(1, 1, device="meta", dtype=torch.bfloat16), out_dtype=torch.float32)
+        return True
+    except (TypeError, RuntimeError, NotImplementedError):
+        return False
+
+
+_MM_TAKES_OUT_DTYPE = _mm_takes_out_dtype()

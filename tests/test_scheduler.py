@@ -278,3 +278,110 @@ def test_abort_gives_everything_back_whatever_the_state():
         run_step(s)
     assert cache.free_pages() == [8]
     assert {r.request_id for r in s.drain_finished()} == {0, 1, 2}
+
+
+def test_no_decoder_waits_for_another_requests_prompt():
+    """A long prompt admitted before three decoding requests must not take their tokens: with a
+    budget of 10 and portions of 8, each decoder gets its token in every step and the prompt
+    takes what is left (continuous_batching.py:91 decodes every running sequence every step)."""
+    cache, s = make(num_pages=64, budget=10, chunk=8, max_concurrent=8)
+    long = req(0, 40, max_new=2)
+    s.add_request(long)
+    run_step(s)                                          # first portion of the long prompt
+    for i in (1, 2, 3):
+        s.add_request(req(i, 2, max_new=12))
+    s.max_num_batched_tokens = 32
+    run_step(s)                                          # admitted, their prompts computed
+    s.max_num_batched_tokens = 10
+    assert [r.request_id for r in s.running] == [0, 1, 2, 3]
+    while long.num_computed < len(long.prompt_tokens):
+        left = len(long.prompt_tokens) - long.num_computed
+        b, _ = run_step(s)
+        got = {i.request.request_id: i.num_tokens for i in b.items}
+        assert got[1] == got[2] == got[3] == 1, got       # nobody skips a step
+        assert got[0] == min(7, left), got                # the prompt takes the rest of the budget
+        assert [i.request.request_id for i in b.items][:3] == [1, 2, 3]
+
+
+def test_budget_of_a_preempted_request_goes_back():
+    """The victim of a preemption may already have its token in the step (decoders are served
+    before portions): its item is dropped and its token is not charged to the budget."""
+    cache, s = make(num_pages=6, page_size=4, budget=6, chunk=4, max_concurrent=4)
+    a, b_ = req(0, 20, max_new=2), req(1, 2, max_new=8)
+    s.add_request(a)
+    s.add_request(b_)
+    for _ in range(4):
+        batch, _ = run_step(s)
+        assert not batch.preempted
+    assert cache.free_pages() == [0] and a.num_computed == 16 and b_.num_tokens == 6
+    batch = s.schedule()          # b's token first, then a's last portion needs a page: b goes
+    assert [r.request_id for r in batch.preempted] == [1]
+    assert [(i.request.request_id, i.num_tokens) for i in batch.items] == [(0, 4)]
+    assert b_.num_computed == 0 and s.waiting[0] is b_
+    s.update(batch, {0: 9})
+    cache.check_consistency()
+    while s.has_unfinished():
+        run_step(s)
+    assert len(a.output_tokens) == 2 and len(b_.output_tokens) == 8
+    assert cache.free_pages() == [6]
+
+
+def make_windowed(window, num_pages, page_size=4, chunk=4, policy="preempt", positions=256):
+    cache = CacheManager([CacheNeeds(paged=PagedKVNeeds(1, 8, window))], [None],
+                         num_pages=num_pages, page_size=page_size, max_requests=4,
+                         max_positions=positions, dtype=torch.float32, device="cpu")
+    return cache, Scheduler(cache, max_concurrent=4, max_num_batched_tokens=16, chunk_size=chunk,
+                            max_positions=positions, policy=policy)
+
+
+@pytest.mark.parametrize("policy", ["preempt", "reserve"])
+def test_windowed_model_is_admitted_where_the_window_fits(policy):
+    """A request far longer than the pool is admitted when every layer reads a window only: it
+    never holds more than ceil((window + portion) / page) + 1 pages."""
+    cache, s = make_windowed(window=8, num_pages=5, policy=policy)
+    r = req(0, 60, max_new=30)                            # 89 positions = 23 pages if all were kept
+    s.add_request(r)
+    most = 0
+    while s.has_unfinished():
+        b, _ = run_step(s)
+        assert not b.preempted
+        most = max(most, 5 - cache.free_pages()[0])
+        cache.check_consistency()
+    assert r.status is RequestStatus.FINISHED and len(r.output_tokens) == 30
+    assert most <= 4
+    # without a window the same request is refused
+    _, s2 = make(num_pages=5, page_size=4)
+    s2.max_positions = 256
+    with pytest.raises(ValueError):
+        s2.add_request(req(0, 60, max_new=30))
+
+
+def test_reserve_policy_counts_windowed_requests_by_their_window():
+    cache, s = make_windowed(window=8, num_pages=8, policy="reserve")
+    for i in range(3):
+        s.add_request(req(i, 30, max_new=10))
+    b, _ = run_step(s)
+    # each request reserves ceil((8 + 4) / 4) + 1 = 4 pages: two fit into 8 pages, the third waits
+    assert [r.request_id for r in b.admitted] == [0, 1] and len(s.waiting) == 1
+
+
+@pytest.mark.parametrize("policy", ["preempt", "reserve"])
+def test_model_with_fixed_state_only(policy):
+    """A model whose mixers keep only fixed-size state has no page group: admission is bounded by
+    the slots alone, under both policies."""
+    from somi_inference_b200.parts.base import StateNeeds
+    cache = CacheManager([CacheNeeds(state=StateNeeds({"s": ((4,), torch.float32)}))], [None],
+                         num_pages=1, page_size=4, max_requests=2, max_positions=64,
+                         dtype=torch.float32, device="cpu")
+    s = Scheduler(cache, max_concurrent=4, max_num_batched_tokens=16, chunk_size=8,
+                  max_positions=64, policy=policy)
+    assert cache.groups == []
+    for i in range(3):
+        s.add_request(req(i, 5, max_new=3))
+    done = []
+    for _ in range(20):
+        if not s.has_unfinished():
+            break
+        _, d = run_step(s)
+        done += d
+    assert sorted(r.request_id for r in done) == [0, 1, 2]
