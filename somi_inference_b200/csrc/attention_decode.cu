@@ -344,9 +344,17 @@ SOMI_API int somi_paged_attention_decode_static(
     if (!somi_decode_supported(nq, nkv, hd) || page_size <= 0 || max_splits <= 0 ||
         n_decode > 65535 || nkv > 65535)
         return SOMI_ERR_UNSUPPORTED;
-    const size_t slots = static_cast<size_t>(n_decode) * nq * max_splits;
-    if (slots > kStaticScratchFloats / (static_cast<size_t>(hd) + 2))
+    // n_decode * nq * max_splits slots of (hd + 2) floats must fit; the test is made with
+    // divisions, so that no product of caller-given numbers can wrap around and pass it
+    const size_t cap_slots = kStaticScratchFloats / (static_cast<size_t>(hd) + 2);
+    if (nq <= 0 || static_cast<size_t>(max_splits) > cap_slots) return SOMI_ERR_SCRATCH_TOO_SMALL;
+    const size_t rows_allowed = cap_slots / static_cast<size_t>(max_splits);     // n_decode * nq
+    if (static_cast<size_t>(nq) > rows_allowed ||
+        static_cast<size_t>(n_decode) > rows_allowed / static_cast<size_t>(nq))
         return SOMI_ERR_SCRATCH_TOO_SMALL;
+    const size_t slots = static_cast<size_t>(n_decode) * nq * max_splits;
+    // The array's address is looked up for the CURRENT device: `stream` must belong to it (as
+    // every pointer argument does); the caller makes that device current before the call.
     int status = 0;
     float* scratch = static_scratch_on_current_device(&status);
     if (scratch == nullptr) return status;

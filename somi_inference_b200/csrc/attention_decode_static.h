@@ -19,6 +19,8 @@
  *  - The first call on a device looks the array's device address up
  *    (cudaGetSymbolAddress, with that device current) and remembers it; later calls on that
  *    device only launch kernels.  Make that first call outside any stream capture.
+ *  - The array that is used is the one of the CURRENT device: make the device that owns
+ *    `stream` and the pointer arguments current before the call.
  *  - The function calls no cudaMalloc, cudaFree or other allocating routine.
  *  - All calls on a device share the one array, which keeps the previous call's contents.
  *    Nothing in it has to start at zero (every slot read is written earlier in the same call),

@@ -68,10 +68,11 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     __shared__ __align__(8) unsigned long long bars[2];
     __shared__ float m_s[kTdWarps][kTdRows], l_s[kTdWarps][kTdRows];
     pdl_launch_dependents();
-    // The kernel before this one wrote the step's own keys and values (one position per request
-    // here) and the queries.  Lengths, block tables and every older cache page were complete
-    // before that kernel started, so their copies are issued before the dependency wait and
-    // fly while it finishes; only the page of the newest position and Q come after the wait.
+    // A kernel of this step wrote the step's own keys and values (one position per request
+    // here) and the queries.  Lengths and block tables [descriptor] and the cache pages of older
+    // positions [old-cache] are written by no kernel of this step, so their copies are issued
+    // before the dependency wait and fly while the predecessor finishes; only the page of the
+    // newest position and Q come after the wait.
 
     const int split = blockIdx.x, kvh = blockIdx.y, i = blockIdx.z;
     const int req = req_base + i, row = row_base + i;

@@ -79,12 +79,22 @@ inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 // Every kernel of this library is launched with the programmatic-serialization attribute: it
 // may be scheduled while its predecessor in the stream is still running, so that its launch
 // latency and its set-up (barriers, tensor memory, index arithmetic) overlap the predecessor's
-// tail.  The rule that makes this safe: a kernel calls `pdl_wait()` before it writes global
-// memory at all, before it reads anything its predecessor writes, and before any early return;
-// it calls `pdl_launch_dependents()` as its first statement so that its own successor may be
-// scheduled.  What only earlier kernels or the host wrote (weights, the step's descriptor, cache
-// pages of older positions) may be read before the wait: every kernel finishes only after its
-// own wait, so everything before the predecessor is complete when the predecessor runs.
+// tail.  A kernel calls `pdl_launch_dependents()` as its first statement, so that its own
+// successor may be scheduled, and `pdl_wait()` before it writes global memory at all and before
+// any early return.  `pdl_wait()` returns when the predecessor has completed; the predecessor
+// completed only after its own wait, so after the wait every earlier kernel is complete.
+//
+// BEFORE the wait nothing of the kind holds: kernel N may be resident while N-1 is still before
+// its own wait and N-2 is running.  So before the wait a kernel may read only memory that NO
+// kernel of the same step writes:
+//   [constant]   model constants (weights, norm weights, inverse frequencies, tensor maps);
+//   [descriptor] the step's descriptor, uploaded by a memcpy that completed before the step's
+//                first kernel started (a copy is not launched programmatically);
+//   [old-cache]  cache slots of positions below the request's cached length of this step: they
+//                were written by earlier steps, and the descriptor copy between two steps is a
+//                full barrier in the stream.
+// Outputs of ANY kernel of the same step (not only the direct predecessor's) are off limits
+// before the wait.  Reads before a wait are tagged with one of the three classes above.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");

@@ -81,8 +81,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     extern __shared__ __align__(16) float row_buf[];
     __shared__ float scratch[33];
     pdl_launch_dependents();
-    // the norm's weight is a constant of the model: a thread's first four columns are fetched
-    // while the kernel before this one finishes
+    // the norm's weight is written by no kernel [constant]: a thread's first four columns are
+    // fetched while the kernel before this one finishes
     F4 w_first = F4{{0.f, 0.f, 0.f, 0.f}};
     if ((H & 3) == 0 && threadIdx.x * 4 < H) w_first = load4_any(weight, weight_dtype, threadIdx.x * 4);
     pdl_wait();
@@ -145,8 +145,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
                                   T* __restrict__ kcache, T* __restrict__ vcache, int page_size) {
     extern __shared__ float cs[];   // cos[rot/2], sin[rot/2]
     pdl_launch_dependents();
-    // positions, frequencies and slots belong to the step's descriptor, not to the kernel before
-    // this one: the angles are ready when the projection is
+    // positions and slots [descriptor] and frequencies [constant] are written by no kernel of
+    // the step: the angles are ready when the projection is
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const float pos = static_cast<float>(positions[t]);
@@ -251,6 +251,7 @@ rope_store_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict_
     extern __shared__ float cs[];                 // per token: cos[rot/2], sin[rot/2]
     __shared__ int slot_s[kRopeToks];
     pdl_launch_dependents();
+    // before the wait: positions and slots [descriptor], frequencies [constant]
     const int t0 = blockIdx.x * kRopeToks;
     const int n_tok = min(kRopeToks, T - t0);
     const int half = rot >> 1;
@@ -328,6 +329,7 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
                                           int heads_per_cta) {
     extern __shared__ float cs[];
     pdl_launch_dependents();
+    // before the wait: positions and slots [descriptor], frequencies [constant]
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int width = (nq + 2 * nkv) * hd;
@@ -339,7 +341,7 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
         cs[half + i] = s;
     }
     const int slot = slot_map ? slot_map[t] : -1;
-    pdl_wait();             // the partial sums are the only input the kernel before this one wrote
+    pdl_wait();             // the partial sums (and the bias add) come after it
     __syncthreads();
     const float* prow = parts + static_cast<size_t>(t) * width;
     auto value = [&](int col) {

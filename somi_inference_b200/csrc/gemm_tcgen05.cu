@@ -124,7 +124,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap w_map,
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_d = tmem_base_s;
-    // Barriers and tensor memory are set up.  The weights do not depend on the preceding kernel,
+    // Barriers and tensor memory are set up.  The weights are written by no kernel [constant],
     // so the producer fills the ring's first stages with W tiles before it waits for that kernel;
     // the activation tiles, and everything any other thread reads or writes, come after the wait.
     const int n_pre = min(nkb, STAGES);

@@ -9,6 +9,7 @@ the cache that earlier steps left, returning float32 logits at the wanted places
 
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Sequence
 
 import torch
@@ -28,6 +29,56 @@ def resolve_dtype(dtype) -> torch.dtype:
         return _DTYPES[dtype]
     except KeyError:
         raise ValueError(f"dtype must be 'bfloat16' or 'float32', got {dtype!r}") from None
+
+
+class LayoutCache:
+    """Which step layouts have a captured graph.  A layout is captured at its second sighting;
+    when `capacity` graphs are held, the one replayed longest ago makes room (a serving run
+    passes through many layouts as requests come, grow and go, and only the recent ones return).
+    """
+
+    def __init__(self, capacity: int, max_sightings: int = 4096) -> None:
+        if capacity < 1:
+            raise ValueError("a layout cache needs room for at least one graph")
+        self.capacity = capacity
+        self.max_sightings = max_sightings
+        self._entries: OrderedDict = OrderedDict()
+        self._seen: dict = {}
+        self.hits = self.captures = self.evictions = 0
+
+    def __len__(self) -> int:
+        return len(self._entries)
+
+    def __contains__(self, key) -> bool:
+        return key in self._entries
+
+    def get(self, key):
+        """The entry captured for `key`, marked as just used; None if there is none."""
+        entry = self._entries.get(key)
+        if entry is not None:
+            self._entries.move_to_end(key)
+            self.hits += 1
+        return entry
+
+    def sighted(self, key) -> bool:
+        """Count an eager run of `key`; True when the layout should be captured now."""
+        if len(self._seen) > self.max_sightings:      # many layouts that never came back
+            self._seen.clear()
+        n = self._seen.get(key, 0) + 1
+        self._seen[key] = n
+        return n >= 2
+
+    def put(self, key, entry) -> None:
+        while len(self._entries) >= self.capacity:
+            old, _ = self._entries.popitem(last=False)     # dropping the graph frees its memory
+            self._seen.pop(old, None)      # it has to be seen twice again before it is captured anew
+            self.evictions += 1
+        self._entries[key] = entry
+        self.captures += 1
+
+    def clear(self) -> None:
+        self._entries.clear()
+        self._seen.clear()
 
 
 class Engine:
@@ -91,13 +142,11 @@ class Engine:
                                     max_positions=self.spec.max_positions)
         self.last_batch: StepBatch | None = None
         self.use_graphs = use_graphs
-        self.max_graphs = 64
         self._token_stage = None
         self._prebuilt = None
         self.token_patch_bytes = 0
         self.graph_max_tokens = 8192     # larger steps are bound by the GPU, not by the host
-        self._graphs: dict[tuple, tuple] = {}
-        self._seen: dict[tuple, int] = {}
+        self._graphs = LayoutCache(capacity=128)
         self._graph_pool = None
         self._graph_generation = self.builder.generation
 
@@ -123,13 +172,14 @@ class Engine:
                 self.cache.reserve(e.request, len(e.tokens))
                 reserved.append(e.request)
             batch, _ = self.builder.build(entries)
+            logits = self._run(batch)
         except Exception:
+            # also when a launch failed: nothing stays reserved, the lengths are as before
             for r in reserved:
                 self.cache.cancel(r)
             for r in registered:
                 self.cache.release(r)
             raise
-        logits = self._run(batch)
         for e in entries:
             self.cache.commit(e.request)
         return logits
@@ -157,7 +207,6 @@ class Engine:
         if self._graph_generation != self.builder.generation:
             # the descriptor buffer moved: graphs captured over the old addresses are void
             self._graphs.clear()
-            self._seen.clear()
             self._graph_generation = self.builder.generation
         key = batch.layout_key
         entry = self._graphs.get(key)
@@ -169,10 +218,7 @@ class Engine:
             return logits.clone() if keep else logits
         with torch.no_grad():
             logits = self.model.forward(batch, self.cache)      # also warms up the libraries
-        if len(self._seen) > 4096:       # many layouts that never came back
-            self._seen.clear()
-        self._seen[key] = self._seen.get(key, 0) + 1
-        if self._seen[key] >= 2 and len(self._graphs) < self.max_graphs:
+        if self._graphs.sighted(key):
             # Capturing runs nothing; recording the same step again is harmless because a step
             # only writes the cache slots of its own tokens, with the same values.
             before = self.ops.launches
@@ -181,7 +227,7 @@ class Engine:
                 static_logits = self.model.forward(batch, self.cache)
             if self._graph_pool is None:
                 self._graph_pool = graph.pool()
-            self._graphs[key] = (graph, static_logits, self.ops.launches - before)
+            self._graphs.put(key, (graph, static_logits, self.ops.launches - before))
             self.ops.launches = before
         return logits
 

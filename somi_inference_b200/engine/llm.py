@@ -100,6 +100,9 @@ class LLM:
     # -------------------------------------------------------------- tokenizer
     def _tok(self):
         if self._tokenizer is None:
+            if not isinstance(self._model_dir, (str, os.PathLike)):
+                raise ValueError("this engine was built from tensors and has no tokenizer: give "
+                                 "prompts as token ids")
             if not any(os.path.isfile(os.path.join(self._model_dir, f))
                        for f in ("tokenizer.json", "tokenizer_config.json", "vocab.json")):
                 raise ValueError("this model folder holds no tokenizer: give prompts as token ids")
@@ -151,20 +154,28 @@ class LLM:
         batch, samplers = cur.batch, cur.samplers
         # the GPU is busy with the step: the host's part of the next one
         self.scheduler.advance(batch)
+        failed_ahead: Exception | None = None
         if self.prepare_early and cur.whole and len(samplers) == len(batch.items):
             nxt = self.scheduler.continue_decoding()
             if nxt is not None:
-                prepared = self.engine.prebuild(
-                    [StepEntry(item.request.request_id, [0], [0]) for item in nxt.items])
-                if (self.run_ahead and cur.ids is not None
-                        and all(r.sampling_params.repetition_penalty == 1.0 for r in samplers)
-                        and len(nxt.items) == len(samplers)
-                        and all(i.request is r for i, r in zip(nxt.items, samplers))):
-                    logits = self.engine.run_prebuilt_fed(prepared, cur.ids, keep=False)
-                    # the token that is still on its way counts for the sampler's counters
-                    self._ahead = self._sample(nxt, samplers, logits, pending=1)
-                else:
-                    self._early = (nxt, prepared)
+                try:
+                    prepared = self.engine.prebuild(
+                        [StepEntry(item.request.request_id, [0], [0]) for item in nxt.items])
+                    if (self.run_ahead and cur.ids is not None
+                            and all(r.sampling_params.repetition_penalty == 1.0 for r in samplers)
+                            and len(nxt.items) == len(samplers)
+                            and all(i.request is r for i, r in zip(nxt.items, samplers))):
+                        logits = self.engine.run_prebuilt_fed(prepared, cur.ids, keep=False)
+                        # the token that is still on its way counts for the sampler's counters
+                        self._ahead = self._sample(nxt, samplers, logits, pending=1)
+                    else:
+                        self._early = (nxt, prepared)
+                except Exception as exc:
+                    # a step that could not be built or launched leaves nothing reserved; the
+                    # step that is running is brought to its end first, then the error is raised
+                    self._ahead = self._early = None
+                    self.scheduler.abandon(nxt)
+                    failed_ahead = exc
         sampled: dict[int, int] = {}
         if cur.ids is not None:
             cur.event.synchronize()
@@ -174,7 +185,10 @@ class LLM:
         self.steps_run += 1
         if self.steps_run % 256 == 0 and hasattr(self.engine.ops, "check_errors"):
             self.engine.ops.check_errors()
-        return self.scheduler.update(batch, sampled, advanced=True)
+        done = self.scheduler.update(batch, sampled, advanced=True)
+        if failed_ahead is not None:
+            raise failed_ahead        # what finished in this step waits in `scheduler.finished`
+        return done
 
     def _launch_next(self) -> "_Launched | None":
         """Schedule and launch a step (or launch the one prepared by the call before, if the
@@ -187,8 +201,12 @@ class LLM:
         if early is not None:
             batch, prepared = early
             samplers = [item.request for item in batch.items]
-            logits = self.engine.run_prebuilt(prepared, [r.output_tokens[-1] for r in samplers],
-                                              keep=False)
+            try:
+                logits = self.engine.run_prebuilt(prepared, [r.output_tokens[-1] for r in samplers],
+                                                  keep=False)
+            except Exception:
+                self.scheduler.abandon(batch)
+                raise
         else:
             batch = self.scheduler.schedule()
             if not batch.items:
@@ -204,8 +222,18 @@ class LLM:
                                          [item.num_tokens - 1] if item.samples else []))
                 if item.samples:
                     samplers.append(item.request)
-            logits = self.engine.run_reserved(entries, keep=False)     # sampled from at once
-        return self._sample(batch, samplers, logits, pending=0)
+            try:
+                logits = self.engine.run_reserved(entries, keep=False)     # sampled from at once
+            except Exception:
+                # the requests stay where the scheduler put them, with nothing reserved: the
+                # next call schedules them again
+                self.scheduler.abandon(batch)
+                raise
+        try:
+            return self._sample(batch, samplers, logits, pending=0)
+        except Exception:
+            self.scheduler.abandon(batch)
+            raise
 
     def _sample(self, batch: ScheduledBatch, samplers: list[Request], logits: torch.Tensor,
                 pending: int) -> "_Launched":

@@ -2,7 +2,12 @@
 
     python -m somi_inference_b200.entrypoints.generate --model-name DIR --prompt-ids 5 17 3 \\
         --max-new-tokens 16 --temperature 0
+    python -m somi_inference_b200.entrypoints.generate --config CONFIG.json --random-weights --seed 0 \
+        --prompt-lens 5 17 33 --max-new-tokens 8 --temperature 0
     python -m somi_inference_b200.entrypoints.generate --write-random-model DIR --config CONFIG.json --seed 0
+
+The second form goes from a configuration and a seed to tokens in one call: the weights are drawn
+as `--write-random-model` would write them and handed to the engine in memory.
 
 The reference ships no command line of its own inside the package; its programs
 are the `python -m benchmarks.bench_*` scripts, whose option names are kept
@@ -51,36 +56,67 @@ def parse_args(argv: list[str] | None = None) -> argparse.Namespace:
     p.add_argument("--write-random-model", type=str, default=None, metavar="DIR",
                    help="Write config.json + model.safetensors with random weights and exit.")
     p.add_argument("--config", type=str, default=None,
-                   help="config.json to take the sizes from (with --write-random-model).")
+                   help="config.json to take the sizes from (with --write-random-model or "
+                        "--random-weights).")
+    p.add_argument("--random-weights", action="store_true",
+                   help="Generate with random weights drawn from --seed for the model of --config "
+                        "(no model folder needed).")
+    p.add_argument("--std", type=float, default=0.02,
+                   help="Standard deviation of the random weights.")
     p.add_argument("--weights-dtype", choices=["float32", "bfloat16"], default="bfloat16")
     p.add_argument("--output-file", type=str, default=None, help="Append results as JSONL.")
     return p.parse_args(argv)
 
 
-def main(argv: list[str] | None = None) -> int:
+def _typed_config(path: str):
+    from ..config.registry import config_class_for
+    with open(path) as f:
+        raw = json.load(f)
+    archs = raw.get("architectures")
+    if not archs:
+        raise ValueError(f"{path}: no 'architectures' list")
+    return config_class_for(archs[0]).from_dict(raw)
+
+
+def main(argv: list[str] | None = None, *, ops=None, device=None) -> int:
+    """`ops` and `device` are for tests that run the command line without a GPU."""
     args = parse_args(argv)
     if args.write_random_model:
         if not args.config:
             print("--write-random-model needs --config", file=sys.stderr)
             return 2
-        from ..config.registry import config_class_for
         from ..weights import write_random_model
-        with open(args.config) as f:
-            raw = json.load(f)
-        cfg = config_class_for(raw["architectures"][0]).from_dict(raw)
-        write_random_model(cfg, args.seed, args.write_random_model,
-                           dtype=getattr(torch, args.weights_dtype))
+        write_random_model(_typed_config(args.config), args.seed, args.write_random_model,
+                           dtype=getattr(torch, args.weights_dtype), std=args.std)
         print(args.write_random_model)
         return 0
-    if not args.model_name:
-        print("--model-name is required", file=sys.stderr)
+    if args.random_weights and not args.config:
+        print("--random-weights needs --config", file=sys.stderr)
         return 2
-    from ..engine import LLM
+    if not args.model_name and not args.random_weights:
+        print("--model-name (or --config with --random-weights) is required", file=sys.stderr)
+        return 2
+    if args.prompt is None and args.prompt_ids is None and args.prompt_lens is None:
+        print("give --prompt, --prompt-ids or --prompt-lens", file=sys.stderr)
+        return 2
+    from ..engine import LLM, Engine
     from ..sampling import SamplingParams
     dtype = "bfloat16" if args.dtype == "auto" else args.dtype
-    llm = LLM(args.model_name, num_blocks=args.num_blocks, block_size=args.block_size,
-              max_concurrent=args.max_concurrent, dtype=dtype, chunk_size=args.chunk_size,
-              max_num_batched_tokens=args.max_num_batched_tokens, policy=args.policy)
+    common = dict(max_concurrent=args.max_concurrent, chunk_size=args.chunk_size,
+                  max_num_batched_tokens=args.max_num_batched_tokens, policy=args.policy)
+    if args.random_weights:
+        from ..weights import random_tensors
+        cfg = _typed_config(args.config)
+        tensors = random_tensors(cfg, args.seed, std=args.std,
+                                 dtype=getattr(torch, args.weights_dtype))
+        engine = Engine.from_tensors(cfg, tensors, dtype=dtype, page_size=args.block_size,
+                                     num_pages=args.num_blocks, max_requests=args.max_concurrent,
+                                     **({"ops": ops} if ops is not None else {}),
+                                     **({"device": device} if device is not None else {}))
+        llm = LLM(engine, **common)
+    else:
+        llm = LLM(args.model_name, num_blocks=args.num_blocks, block_size=args.block_size,
+                  dtype=dtype, ops=ops, device=device, **common)
     kw = dict(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
               repetition_penalty=args.repetition_penalty)
     results = []
@@ -98,9 +134,6 @@ def main(argv: list[str] | None = None) -> int:
         outs = llm.generate_many(prompts, max_new_tokens=args.max_new_tokens, sampling_params=sps,
                                  ignore_eos=True)
         results = [{"prompt_len": n, "output_ids": o} for n, o in zip(args.prompt_lens, outs)]
-    else:
-        print("give --prompt, --prompt-ids or --prompt-lens", file=sys.stderr)
-        return 2
     for r in results:
         print(json.dumps(r))
     if args.output_file:

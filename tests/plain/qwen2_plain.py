@@ -8,7 +8,7 @@ tensor operations only.
 
 Its agreement with the reference's own model code on a tiny random model is
 recorded under tests/golden/ (made by tests/golden/make_golden.py) and checked
-by tests/test_plain_golden.py.
+by tests/test_plain.py.
 """
 
 from __future__ import annotations

@@ -1,7 +1,7 @@
 """The host side of the engine (batch layout, cache manager, order of runs, scheduler loop)
 checked on the CPU by handing the engine the test-only kernel table of tests/plain/host_ops.py.
 The product path never runs like this; the same checks run on the GPU with the CUDA kernels in
-tests/test_gpu_replay.py and tests/test_gpu_toy.py."""
+tests/test_gpu_replay.py and tests/test_gpu_engine.py."""
 
 import pytest
 import torch
@@ -80,6 +80,25 @@ def test_generation_through_the_entry_point_matches_plain_greedy(root):
     assert llm.generate(prompts[1], max_new_tokens=4, temperature=0.0) == outs[1][:4]
 
 
+def test_sampled_generation_matches_the_plain_sampler(root):
+    """Tiny B at temperature 0.7 with top-k, top-p and a repetition penalty, portions of 32 mixed
+    with decoding: every token is the one the plain pipeline draws with the same (seed, counter)."""
+    from tests.plain import generate_plain
+    d = make_model("B", root, torch.float32, std=0.02)
+    cfg, w = plain.load_folder(d)
+    llm = LLM(d, num_blocks=64, block_size=8, max_concurrent=4, device="cpu", dtype="float32",
+              ops=HostOps(), chunk_size=32, max_num_batched_tokens=40)
+    prompts = [random_tokens(n, 1000, 90 + i) for i, n in enumerate([1, 9, 40, 100])]
+    kinds = [dict(temperature=0.7), dict(temperature=0.7, top_k=40),
+             dict(temperature=0.7, top_p=0.9), dict(temperature=0.7, repetition_penalty=1.3)]
+    sps = [SamplingParams(seed=5 + i, **k) for i, k in enumerate(kinds)]
+    outs = llm.generate_many(prompts, max_new_tokens=6, sampling_params=sps, ignore_eos=True,
+                             arrival_steps=[0, 0, 1, 2])
+    for p, o, sp, k in zip(prompts, outs, sps, kinds):
+        assert generate_plain.check_sampled(cfg, w, p, o, seed=sp.seed, **k) == 0
+        assert o == generate_plain.generate(cfg, w, p, 6, seed=sp.seed, **k)
+
+
 def test_end_of_sequence_under_steps_launched_ahead(root):
     """Decode steps are launched before the host has read the ids of the step before.  A request
     that ends on such a token has a row in the step that ran ahead: the row is dropped, the others
@@ -130,6 +149,63 @@ def test_preempted_request_generates_the_same_tokens(root):
     assert sum(r.num_preemptions for r in reqs) > 0, "the test is meant to run out of pages"
     assert [r.output_tokens for r in reqs] == want
     assert tight.engine.cache.free_pages() == [28]
+
+
+class FailingOps(HostOps):
+    """A kernel table whose attention raises at chosen calls, like a launch that failed."""
+
+    def __init__(self, fail_at: set[int]) -> None:
+        super().__init__()
+        self.calls = 0
+        self.fail_at = set(fail_at)
+
+    def paged_attention(self, *args, **kwargs):
+        self.calls += 1
+        if self.calls in self.fail_at:
+            raise RuntimeError("injected launch failure")
+        return super().paged_attention(*args, **kwargs)
+
+
+def test_a_failed_launch_leaves_nothing_reserved(root):
+    """If a step raises after its pages were reserved (a kernel error, out of memory), the
+    reservations are cancelled: the engine's step leaves the cache as it was, and the loop of
+    the entry point can simply be called again and generates what it would have generated."""
+    d = make_model("A", root, torch.float32, std=0.08)
+    cfg, w = plain.load_folder(d)
+    eng = Engine(d, dtype="float32", page_size=16, num_pages=8, device="cpu", ops=FailingOps({3}))
+    eng.step([StepEntry("a", random_tokens(20, 256, 1), [])])
+    free = eng.cache.free_pages()
+    with pytest.raises(RuntimeError, match="injected"):
+        eng.step([StepEntry("a", random_tokens(20, 256, 2), []), StepEntry("b", [3, 4, 5], [2])])
+    assert eng.cache.free_pages() == free and eng.cache.length("a") == 20
+    assert not eng.cache.is_registered("b")
+    eng.cache.check_consistency()
+    eng.step([StepEntry("a", random_tokens(20, 256, 2), []), StepEntry("b", [3, 4, 5], [2])])
+
+    prompts = [random_tokens(n, 256, 90 + i) for i, n in enumerate([9, 21])]
+    want = [plain.greedy(cfg, w, p, 8) for p in prompts]
+    layers = cfg["num_hidden_layers"]
+    # failures in a prompt step, in a decode step launched ahead, and in a later one
+    for fail_at in ({1}, {2 * layers + 1}, {5 * layers + 2}):
+        llm = LLM(d, num_blocks=16, block_size=8, max_concurrent=2, device="cpu", dtype="float32",
+                  ops=FailingOps(fail_at), chunk_size=32)
+        reqs = [llm.make_request(p, max_new_tokens=8, sampling_params=SamplingParams(temperature=0.0))
+                for p in prompts]
+        for r in reqs:
+            llm.scheduler.add_request(r)
+        failures = 0
+        for _ in range(200):
+            if not llm.scheduler.has_unfinished():
+                break
+            try:
+                llm.step()
+            except RuntimeError:
+                failures += 1
+            llm.engine.cache.check_consistency()
+        assert failures == 1
+        assert [r.output_tokens for r in reqs] == want, fail_at
+        llm.step()
+        assert llm.engine.cache.free_pages() == [16]
 
 
 def test_toy_architecture_is_registered_built_and_stepped(root):

@@ -36,6 +36,31 @@ def test_greedy_generation_through_the_entry_point(root, name):
     assert llm.generate(prompts[2], max_new_tokens=5, temperature=0.0) == outs[2][:5]
 
 
+def test_tiny_b_as_the_benchmark_description_states_it(root):
+    """Tiny B of the benchmark description, to the letter: weights N(0, 0.02) from seed 1,
+    float32, pages of 8, four prompts of 1/9/40/100 random ids, prompt portions of 32 tokens
+    mixed with decoding, 12 tokens each at temperature 0.7 with fixed sampling seeds.  Expected
+    ids: plain whole-sequence logits through the plain sampler with the same (seed, counter)
+    (the reference checks generation against an independent implementation in
+    tests/entrypoints/test_llm_e2e.py:60-71)."""
+    from somi_inference_b200 import LLM, SamplingParams
+    from tests.plain import generate_plain
+    d = make_model("B", root, torch.float32, std=0.02)
+    cfg, w = plain.load_folder(d)
+    llm = LLM(d, num_blocks=64, block_size=8, max_concurrent=4, dtype="float32", chunk_size=32,
+              max_num_batched_tokens=40)
+    prompts = [random_tokens(n, 1000, 90 + i) for i, n in enumerate([1, 9, 40, 100])]
+    sps = [SamplingParams(temperature=0.7, seed=5 + i) for i in range(4)]
+    outs = llm.generate_many(prompts, max_new_tokens=12, sampling_params=sps, ignore_eos=True,
+                             arrival_steps=[0, 0, 1, 2])
+    boundary = 0
+    for p, o, sp in zip(prompts, outs, sps):
+        assert len(o) == 12
+        boundary += generate_plain.check_sampled(cfg, w, p, o, temperature=0.7, seed=sp.seed)
+    assert boundary <= 1          # 48 draws: a draw at a rounding boundary is a rare event
+    assert llm.engine.cache.free_pages() == [64]
+
+
 def test_temperature_generation_is_reproducible_and_batch_independent(root):
     from somi_inference_b200 import LLM, SamplingParams
     d = make_model("B", root, torch.bfloat16, std=STD)
