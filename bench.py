@@ -193,6 +193,8 @@ def build_engine(shape: str, layers: int, max_tokens: int, max_requests: int, po
     gen = torch.Generator(device="cuda").manual_seed(0)
     tensors = {}
     for name, d in declared_tensors(cfg.to_model_spec()).items():
+        if d.ignored:
+            continue
         if d.init == "ones":
             tensors[name] = torch.ones(d.shape, dtype=torch.bfloat16, device="cuda")
         else:

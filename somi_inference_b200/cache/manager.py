@@ -8,10 +8,13 @@ block list and token count, two-phase use (`allocate_slots` before the forward,
 
 What this manager does differently:
 
-* Runs of the schedule are put into *groups* by what they need (kv heads, head
-  size, window).  Each group has its own page pool, its own device tensor
-  `[runs_in_group, 2, num_pages, kv_heads, page_size, head_dim]` and its own
-  block table per request.  Runs that attend over all keys and runs that only
+* Runs of the schedule are put into *groups* by what they need (kv heads, key
+  width, value width, window).  Each group has its own page pool, its own device
+  storage and its own block table per request.  Where keys and values have the
+  same width the storage is one tensor `[runs_in_group, 2, num_pages, kv_heads,
+  page_size, head_dim]` (a page of one kv head is contiguous, and one tensor map
+  covers keys and values); where they differ, keys and values are two tensors
+  `[runs_in_group, num_pages, kv_heads, page_size, width]`.  Runs that attend over all keys and runs that only
   ever read a window therefore never compete for, or waste, each other's pages.
 * A window group gives pages back as soon as every position in them has fallen
   out of the window (`commit`); the block table keeps -1 in their place.
@@ -41,10 +44,12 @@ class PagedView:
 
     group: int                 # index into StepBatch.groups
     keys: torch.Tensor         # [num_pages, kv_heads, page_size, head_dim]
-    values: torch.Tensor       # same shape
+    values: torch.Tensor       # [num_pages, kv_heads, page_size, value width]
     page_size: int
     window: int | None
-    storage: torch.Tensor | None = None   # the group's whole tensor (for tensor maps over it)
+    # the group's whole tensor, for tensor maps over keys and values at once; None where keys
+    # and values differ in width and are stored apart
+    storage: torch.Tensor | None = None
 
 
 @dataclass
@@ -61,9 +66,17 @@ class _Group:
         self.runs = runs
         self.pool = PagePool(num_pages)
         self.page_size = page_size
-        self.storage = torch.zeros(
-            (len(runs), 2, num_pages, needs.num_kv_heads, page_size, needs.head_dim),
-            dtype=dtype, device=device)
+        if needs.value_width == needs.head_dim:
+            self.storage = torch.zeros(
+                (len(runs), 2, num_pages, needs.num_kv_heads, page_size, needs.head_dim),
+                dtype=dtype, device=device)
+            self.keys, self.values = self.storage[:, 0], self.storage[:, 1]
+        else:
+            self.storage = None
+            self.keys = torch.zeros((len(runs), num_pages, needs.num_kv_heads, page_size,
+                                     needs.head_dim), dtype=dtype, device=device)
+            self.values = torch.zeros((len(runs), num_pages, needs.num_kv_heads, page_size,
+                                       needs.value_width), dtype=dtype, device=device)
         # host block tables, one row per state slot (= per live request)
         self.tables = np.full((max_requests, max_blocks), FREED, dtype=np.int32)
         self.first_live = np.zeros(max_requests, dtype=np.int64)  # first block not yet given back
@@ -98,7 +111,8 @@ class CacheManager:
         for run, (needs, owner) in enumerate(zip(needs_per_run, owner_of_run)):
             if owner is None and needs is not None and needs.paged is not None:
                 p = needs.paged
-                by_key.setdefault((p.num_kv_heads, p.head_dim, p.window), []).append(run)
+                by_key.setdefault((p.num_kv_heads, p.head_dim, p.window, p.value_width),
+                                  []).append(run)
         for key, runs in by_key.items():
             needs = PagedKVNeeds(*key)
             self.groups.append(_Group(needs, runs, num_pages, page_size, max_requests,
@@ -111,8 +125,8 @@ class CacheManager:
                 for gi, g in enumerate(self.groups):
                     if run in g.runs:
                         r = g.runs.index(run)
-                        view.paged = PagedView(gi, g.storage[r, 0], g.storage[r, 1],
-                                               page_size, g.needs.window, g.storage)
+                        view.paged = PagedView(gi, g.keys[r], g.values[r], page_size,
+                                               g.needs.window, g.storage)
             if needs.state is not None:
                 for name, (shape, sdtype) in needs.state.tensors.items():
                     view.state[name] = torch.zeros((max_requests, *shape), dtype=sdtype,

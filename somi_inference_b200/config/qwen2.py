@@ -188,10 +188,11 @@ class Qwen2Config:
                                      "names": {"gate_weight": f"{p}.mlp.gate_proj.weight",
                                                "up_weight": f"{p}.mlp.up_proj.weight",
                                                "down_weight": f"{p}.mlp.down_proj.weight"}})
-            layers.append(LayerSpec(prefix=p, mixer=mixer, feed_forward=ff,
-                                    mixer_norm=norm(f"{p}.input_layernorm.weight"),
-                                    feed_forward_norm=norm(f"{p}.post_attention_layernorm.weight"),
-                                    arrangement="pre_norm"))
+            layers.append(LayerSpec(
+                prefix=p, mixer=mixer, feed_forward=ff,
+                norms={"mixer": norm(f"{p}.input_layernorm.weight"),
+                       "feed_forward": norm(f"{p}.post_attention_layernorm.weight")},
+                arrangement="pre_norm"))
         spec = ModelSpec(
             architecture=ARCHITECTURE, hidden_size=self.hidden_size,
             vocab_size=self.vocab_size, max_positions=self.max_position_embeddings,

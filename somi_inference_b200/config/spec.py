@@ -11,7 +11,7 @@ this file knows an architecture; an architecture's config class produces a
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any
+from typing import Any, Mapping
 
 
 @dataclass(frozen=True)
@@ -29,13 +29,19 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One decoder layer: weight-name prefix, its parts and their arrangement."""
+    """One decoder layer: weight-name prefix, its parts and their arrangement.
+
+    A layer has at most one mixer and at most one feed-forward (either may be None) and any
+    number of norms, each under the name by which the layer's arrangement asks for it: the
+    pre-norm arrangement wants "mixer" and "feed_forward"; an arrangement that also normalises
+    what its parts return can name four.  The arrangement's constructor is called with
+    `(mixer, feed_forward, norms)`, `norms` being a dict from those names to built norms.
+    """
 
     prefix: str  # e.g. "model.layers.3"
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    mixer: PartSpec | None
+    feed_forward: PartSpec | None
+    norms: Mapping[str, PartSpec] = field(default_factory=dict)
     arrangement: str = "pre_norm"
 
 

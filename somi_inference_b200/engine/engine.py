@@ -93,11 +93,7 @@ class Engine:
         """
         config = load_config(model_dir)
         spec = config.to_model_spec()
-        declared = declared_tensors(spec)
-        optional = ()
-        if spec.head.params.get("tied"):
-            optional = (spec.head.params["names"]["weight"],)
-        tensors = load_tensors(model_dir, declared, optional=optional)
+        tensors = load_tensors(model_dir, declared_tensors(spec))
         self._setup(config, tensors, dtype=dtype, page_size=page_size, num_pages=num_pages,
                     max_tokens=max_tokens, max_requests=max_requests, device=device, ops=ops,
                     use_graphs=use_graphs)

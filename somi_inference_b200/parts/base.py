@@ -20,8 +20,11 @@ Interfaces (duck-typed; the classes below only document them):
                  `cache_needs()`; `owns_cache` is False when the run reads
                  another run's cache and must not write it.
 * PositionEncoding: `encode_and_store(qkv, geometry, batch, paged, write)`.
-* Block arrangement: `forward(residual, pending, batch, cache, owns_cache)`
-                 returns the delta that the next norm has to add.
+* Embedding:     `forward(batch) -> Tensor` float32 [T, H]: the residual stream's start, from
+                 `batch.token_ids` (and whatever else of the batch it needs: positions, ...).
+* Block arrangement: built as `cls(mixer, feed_forward, norms)` (`norms`: name -> norm; a
+                 part the layer does not have is None); `forward(residual, pending, batch,
+                 cache, owns_cache)` returns the delta that the next norm has to add.
 """
 
 from __future__ import annotations
@@ -40,6 +43,9 @@ class TensorDecl:
     shape: tuple[int, ...]
     init: str = "normal"          # "normal" | "ones" | "zeros": used by the random-weights mode
     matrix: bool = True           # matrices feed GEMMs and are held in the compute dtype
+    optional: bool = False        # the file may lack it; the part then finds no such name
+    ignored: bool = False         # tolerated in the file (shape-checked) but never read: a
+                                  # redundant copy, such as the head's matrix of a tied model
 
 
 @dataclass
@@ -70,8 +76,13 @@ class PagedKVNeeds:
     """Keys and values that grow with the sequence, kept in pages."""
 
     num_kv_heads: int
-    head_dim: int
+    head_dim: int                 # width of a key
     window: int | None = None     # None: all keys; n: only the last n positions are ever read
+    value_dim: int | None = None  # width of a value; None: the same as a key's
+
+    @property
+    def value_width(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)

@@ -14,11 +14,16 @@ from .registry import ARRANGEMENTS
 
 @ARRANGEMENTS.register("pre_norm")
 class PreNormBlock:
-    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm) -> None:
+    def __init__(self, mixer, feed_forward, norms) -> None:
+        if mixer is None or feed_forward is None:
+            raise ValueError("the pre-norm arrangement needs a mixer and a feed-forward")
+        if set(norms) != {"mixer", "feed_forward"}:
+            raise ValueError("the pre-norm arrangement takes the norms 'mixer' and "
+                             f"'feed_forward', got {sorted(norms)}")
         self.mixer = mixer
         self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+        self.mixer_norm = norms["mixer"]
+        self.feed_forward_norm = norms["feed_forward"]
 
     def forward(self, residual, pending, batch, cache, owns_cache):
         h = self.mixer_norm.forward(residual, pending)

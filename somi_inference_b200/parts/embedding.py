@@ -27,7 +27,8 @@ class TokenEmbedding:
         self.weight = tensors[names_of(params)["weight"]]
         self.hidden = int(params["hidden_size"])
 
-    def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, batch) -> torch.Tensor:
+        token_ids = batch.token_ids
         out = torch.empty((token_ids.shape[0], self.hidden), dtype=torch.float32,
                           device=token_ids.device)
         self.ctx.ops.embed(token_ids, self.weight, out)
@@ -38,10 +39,11 @@ class TokenEmbedding:
 class LMHead:
     @staticmethod
     def declare(params) -> list[TensorDecl]:
-        if params["tied"]:
-            return []
-        return [TensorDecl(names_of(params)["weight"],
-                           (int(params["vocab_size"]), int(params["hidden_size"])))]
+        shape = (int(params["vocab_size"]), int(params["hidden_size"]))
+        # a tied model's file may still carry the head's matrix (the reference drops it as well:
+        # somi_inference/models/qwen2_adapter.py:161-162): tolerated, never read
+        return [TensorDecl(names_of(params)["weight"], shape, optional=bool(params["tied"]),
+                           ignored=bool(params["tied"]))]
 
     def __init__(self, params, tensors, ctx: BuildContext) -> None:
         n = names_of(params)

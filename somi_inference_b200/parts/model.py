@@ -29,10 +29,12 @@ def declared_tensors(spec: ModelSpec) -> dict[str, TensorDecl]:
 
     add(EMBEDDINGS.declare(spec.embedding))
     for layer in spec.layers:
-        add(MIXERS.declare(layer.mixer))
-        add(FEED_FORWARDS.declare(layer.feed_forward))
-        add(NORMS.declare(layer.mixer_norm))
-        add(NORMS.declare(layer.feed_forward_norm))
+        if layer.mixer is not None:
+            add(MIXERS.declare(layer.mixer))
+        if layer.feed_forward is not None:
+            add(FEED_FORWARDS.declare(layer.feed_forward))
+        for norm in layer.norms.values():
+            add(NORMS.declare(norm))
     add(NORMS.declare(spec.final_norm))
     add(HEADS.declare(spec.head))
     return out
@@ -44,7 +46,11 @@ class Decoder:
         self.spec = spec
         self.ctx = ctx
         decls = declared_tensors(spec)
-        placed = {name: ctx.place(tensors[name], matrix=d.matrix) for name, d in decls.items()}
+        lacking = [n for n, d in decls.items() if n not in tensors and not (d.optional or d.ignored)]
+        if lacking:
+            raise KeyError(f"tensors missing for the model: {', '.join(sorted(lacking))}")
+        placed = {name: ctx.place(tensors[name], matrix=d.matrix) for name, d in decls.items()
+                  if name in tensors and not d.ignored}
         self.embedding = EMBEDDINGS.build(spec.embedding, placed, ctx)
         self.layers = [self._build_layer(layer, placed) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, placed, ctx)
@@ -52,24 +58,27 @@ class Decoder:
         self.schedule = spec.schedule
         # a step can be captured in a CUDA graph only if no part plans on the host per step
         self.graph_safe = all(getattr(p, "graph_safe", False)
-                              for b in self.layers for p in (b.mixer, b.feed_forward))
+                              for b in self.layers for p in (b.mixer, b.feed_forward)
+                              if p is not None)
 
     def _build_layer(self, layer: LayerSpec, placed):
-        return ARRANGEMENTS.get(layer.arrangement)(
-            MIXERS.build(layer.mixer, placed, self.ctx),
-            FEED_FORWARDS.build(layer.feed_forward, placed, self.ctx),
-            NORMS.build(layer.mixer_norm, placed, self.ctx),
-            NORMS.build(layer.feed_forward_norm, placed, self.ctx))
+        mixer = None if layer.mixer is None else MIXERS.build(layer.mixer, placed, self.ctx)
+        ff = (None if layer.feed_forward is None
+              else FEED_FORWARDS.build(layer.feed_forward, placed, self.ctx))
+        norms = {name: NORMS.build(spec, placed, self.ctx) for name, spec in layer.norms.items()}
+        return ARRANGEMENTS.get(layer.arrangement)(mixer, ff, norms)
 
     def cache_needs(self) -> tuple[list[CacheNeeds | None], list[int | None]]:
-        """Per run of the schedule: what its mixer needs, and whose cache it reads."""
-        needs = [self.layers[run.layer].mixer.cache_needs() for run in self.schedule]
+        """Per run of the schedule: what its mixer needs (None: no mixer, or nothing), and
+        whose cache it reads."""
+        mixers = [self.layers[run.layer].mixer for run in self.schedule]
+        needs = [None if m is None else m.cache_needs() for m in mixers]
         owners = [run.cache_of for run in self.schedule]
         return needs, owners
 
     def forward(self, batch, cache) -> torch.Tensor:
         """Run the step's tokens; return float32 logits [len(batch.logit_rows), vocab]."""
-        residual = self.embedding.forward(batch.token_ids)
+        residual = self.embedding.forward(batch)
         pending = None
         for i, run in enumerate(self.schedule):
             pending = self.layers[run.layer].forward(residual, pending, batch, cache.view(i),

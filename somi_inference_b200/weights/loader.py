@@ -59,15 +59,16 @@ def _open_files(model_dir: str) -> dict[str, SafetensorsFile]:
 
 def load_tensors(model_dir: str, declared: Mapping[str, TensorDecl],
                  optional: tuple[str, ...] = ()) -> dict[str, torch.Tensor]:
-    """Return {name: CPU tensor in its stored dtype} for every declared tensor.
+    """Return {name: CPU tensor in its stored dtype} for every declared tensor that is read.
 
-    `optional` names may be present in the file without being declared (a tied
-    model's redundant `lm_head.weight`, which the reference drops as well:
-    somi_inference/models/qwen2_adapter.py:161-162).
+    A declaration marked `optional` may be absent from the file (it is then absent from the
+    result); one marked `ignored` is checked for its shape when present but never read.  Names
+    in `optional` may be present in the file without being declared at all.
     """
     files = _open_files(model_dir)
     present = {n for n in files if not n.endswith(_IGNORED_SUFFIXES)}
-    missing = sorted(n for n in declared if n not in present)
+    missing = sorted(n for n, d in declared.items()
+                     if n not in present and not (d.optional or d.ignored))
     unexpected = sorted(n for n in present if n not in declared and n not in optional)
     wrong = []
     for name in sorted(present & set(declared)):
@@ -76,4 +77,5 @@ def load_tensors(model_dir: str, declared: Mapping[str, TensorDecl],
             wrong.append((name, shape, declared[name].shape))
     if missing or unexpected or wrong:
         raise WeightError(missing, unexpected, wrong, model_dir)
-    return {name: files[name].tensor(name) for name in declared}
+    return {name: files[name].tensor(name) for name, d in declared.items()
+            if name in present and not d.ignored}

@@ -25,6 +25,8 @@ def random_tensors(config, seed: int, *, std: float = 0.02,
     gen.manual_seed(int(seed))
     out: dict[str, torch.Tensor] = {}
     for name, decl in declared_tensors(config.to_model_spec()).items():
+        if decl.ignored:
+            continue
         if decl.init == "ones":
             t = torch.ones(decl.shape, dtype=torch.float32)
         elif decl.init == "zeros":

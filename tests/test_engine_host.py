@@ -216,7 +216,10 @@ def test_toy_architecture_is_registered_built_and_stepped(root):
         ids = random_tokens(45, toy_model.V, 3)
         ref = toy_model.plain_logits(d, ids)
         eng = Engine(d, dtype="float32", page_size=8, max_tokens=128, device="cpu", ops=HostOps())
-        assert len(eng.cache.groups) == 2                      # full keys, and a window of 6
+        # full keys (two layers share the group), a window of 6, and keys and values of
+        # different widths stored apart
+        assert len(eng.cache.groups) == 3
+        assert [g.storage is None for g in eng.cache.groups].count(True) == 1
         got = eng.step([StepEntry("w", ids, list(range(45)))])
         assert (got - ref).abs().max().item() < 3e-5
         eng.end("w")
@@ -228,6 +231,14 @@ def test_toy_architecture_is_registered_built_and_stepped(root):
         assert (torch.cat(rows) - ref).abs().max().item() < 3e-5
         eng.end("p")
         assert all(f == eng.num_pages for f in eng.cache.free_pages())
+        # the same model with the tensor that its file may lack (a bias) present
+        d2 = toy_model.write_toy_model(root + "/toy_bias", with_optional=True)
+        ref2 = toy_model.plain_logits(d2, ids)
+        assert (ref2 - ref).abs().max().item() > 1e-3          # the bias matters
+        eng2 = Engine(d2, dtype="float32", page_size=8, max_tokens=128, device="cpu", ops=HostOps())
+        got2 = torch.cat([eng2.step([StepEntry("q", ids[:30], list(range(30)))]),
+                          eng2.step([StepEntry("q", ids[30:], list(range(15)))])])
+        assert (got2 - ref2).abs().max().item() < 3e-5
     finally:
         unregister_architecture(toy_model.ARCH)
         unregister_toys()

@@ -302,8 +302,10 @@ def test_parts_alone(root):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_toy_architecture_on_the_gpu(root, dtype):
-    """A mixer with state of its own, a routed feed-forward and another position encoding, all
-    defined by the tests, run through the engine with the CUDA kernels for everything else."""
+    """A mixer with state of its own, a routed feed-forward, another position encoding, an
+    embedding that reads positions, a layer with four norms, a layer without a feed-forward and
+    a mixer whose values are wider than its keys, all defined by the tests, run through the
+    engine with the CUDA kernels for everything else."""
     from somi_inference_b200.config import register_architecture, unregister_architecture
     from somi_inference_b200.engine import Engine, StepEntry
     register_toys()
@@ -319,7 +321,7 @@ def test_toy_architecture_on_the_gpu(root, dtype):
         for mode in (replay.whole, replay.portions, replay.mixed):
             steps, max_tokens = mode(reqs)
             eng = Engine(d, dtype=dtype, page_size=8, max_tokens=max_tokens)
-            assert len(eng.cache.groups) == 2
+            assert len(eng.cache.groups) == 3
             got = replay.run_steps(eng, steps)
             replay.compare(got, ref, atol, f"toy/{dtype}/{mode.__name__}", rms)
             assert all(f == eng.num_pages for f in eng.cache.free_pages())

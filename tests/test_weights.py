@@ -92,9 +92,13 @@ def test_tied_model_tolerates_lm_head_and_untied_needs_it(tmp_path):
     os.makedirs(tmp_path / "tied")
     save_safetensors(t, str(tmp_path / "tied" / "model.safetensors"))
     decl = declared_tensors(cfg.to_model_spec())
-    with pytest.raises(WeightError):
-        load_tensors(str(tmp_path / "tied"), decl)
-    assert "lm_head.weight" not in load_tensors(str(tmp_path / "tied"), decl, optional=("lm_head.weight",))
+    # the tied model's head declares the matrix as a copy that is tolerated and never read
+    assert "lm_head.weight" not in load_tensors(str(tmp_path / "tied"), decl)
+    t["lm_head.weight"] = torch.zeros(3, 3)                   # but its shape is still checked
+    os.makedirs(tmp_path / "tied_bad")
+    save_safetensors(t, str(tmp_path / "tied_bad" / "model.safetensors"))
+    with pytest.raises(WeightError, match="wrong shape"):
+        load_tensors(str(tmp_path / "tied_bad"), decl)
     cfg_b = Qwen2Config.from_dict(TINY_B)
     tb = random_tensors(cfg_b, 1, dtype=torch.float32)
     del tb["lm_head.weight"]
@@ -102,6 +106,23 @@ def test_tied_model_tolerates_lm_head_and_untied_needs_it(tmp_path):
     save_safetensors(tb, str(tmp_path / "untied" / "model.safetensors"))
     with pytest.raises(WeightError, match="lm_head.weight"):
         load_tensors(str(tmp_path / "untied"), declared_tensors(cfg_b.to_model_spec()))
+
+
+def test_optional_tensor_may_be_absent(tmp_path):
+    """A declaration marked optional: absent from the file -> absent from the result, no error;
+    present -> loaded and shape-checked like any other."""
+    from somi_inference_b200.parts.base import TensorDecl
+    decl = {"w": TensorDecl("w", (2, 3)), "b": TensorDecl("b", (2,), matrix=False, optional=True)}
+    os.makedirs(tmp_path / "without")
+    save_safetensors({"w": torch.ones(2, 3)}, str(tmp_path / "without" / "model.safetensors"))
+    assert sorted(load_tensors(str(tmp_path / "without"), decl)) == ["w"]
+    os.makedirs(tmp_path / "with")
+    save_safetensors({"w": torch.ones(2, 3), "b": torch.ones(2)}, str(tmp_path / "with" / "model.safetensors"))
+    assert sorted(load_tensors(str(tmp_path / "with"), decl)) == ["b", "w"]
+    os.makedirs(tmp_path / "bad")
+    save_safetensors({"w": torch.ones(2, 3), "b": torch.ones(5)}, str(tmp_path / "bad" / "model.safetensors"))
+    with pytest.raises(WeightError, match="wrong shape"):
+        load_tensors(str(tmp_path / "bad"), decl)
 
 
 def test_sharded_folder(tmp_path):

@@ -7,6 +7,12 @@ or position encoding without a change to its files.  None of them is anybody's m
 * `ToyRoutedFF`: a feed-forward with routing: top-1 of `n_experts` tiny SwiGLU-free experts,
   router logits in float32.
 * `ToyShiftEncoding`: a position encoding that adds position * step to one key/query dim.
+* `ToyWideValueMixer`: attention whose values are wider than its keys (the cache keeps keys and
+  values of different widths), with its own gather over the block table and an optional bias.
+* `ToyPositionEmbedding`: an embedding that adds a learned row per position (needs the batch's
+  positions, not only its token ids).
+* `ToySandwichBlock`: an arrangement with four norms (before and after each part);
+  `ToyMixerOnlyBlock`: a layer without a feed-forward.
 Each has its plain whole-sequence formula beside it.
 """
 
@@ -14,8 +20,10 @@ from __future__ import annotations
 
 import torch
 
-from somi_inference_b200.parts import FEED_FORWARDS, MIXERS, POSITION_ENCODINGS
-from somi_inference_b200.parts.base import CacheNeeds, StateNeeds, TensorDecl, names_of
+from somi_inference_b200.parts import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, MIXERS,
+                                       POSITION_ENCODINGS)
+from somi_inference_b200.parts.base import (CacheNeeds, PagedKVNeeds, StateNeeds, TensorDecl,
+                                            names_of)
 
 
 class ToyDecayMixer:
@@ -108,13 +116,134 @@ class ToyShiftEncoding:
                                 0, group.slot_map if write else None, paged.keys, paged.values)
 
 
+class ToyWideValueMixer:
+    """Causal attention with `heads` heads over one key/value head: keys of width `key_dim`,
+    values of width `value_dim` (not the same), no position encoding, an output bias that the
+    weight file may lack.  It writes and gathers its pages itself, with tensor indexing, and
+    plans on the host (so its steps are not captured in graphs)."""
+
+    graph_safe = False
+
+    @staticmethod
+    def declare(params):
+        n = names_of(params)
+        h, nh = int(params["hidden_size"]), int(params["heads"])
+        kd, vd = int(params["key_dim"]), int(params["value_dim"])
+        return [TensorDecl(n["wq"], (nh * kd, h)), TensorDecl(n["wk"], (kd, h)),
+                TensorDecl(n["wv"], (vd, h)), TensorDecl(n["wo"], (h, nh * vd)),
+                TensorDecl(n["bo"], (h,), matrix=False, optional=True)]
+
+    def __init__(self, params, tensors, ctx):
+        n = names_of(params)
+        self.nh, self.kd, self.vd = int(params["heads"]), int(params["key_dim"]), int(params["value_dim"])
+        self.wq, self.wk = tensors[n["wq"]].float(), tensors[n["wk"]].float()
+        self.wv, self.wo = tensors[n["wv"]].float(), tensors[n["wo"]].float()
+        self.bo = tensors[n["bo"]].float() if n["bo"] in tensors else None
+
+    def cache_needs(self):
+        return CacheNeeds(paged=PagedKVNeeds(1, self.kd, None, value_dim=self.vd))
+
+    def forward(self, x, batch, cache, owns_cache):
+        paged = cache.paged
+        group = batch.groups[paged.group]
+        ps = paged.page_size
+        xf = x.float()
+        T = xf.shape[0]
+        q = (xf @ self.wq.T).view(T, self.nh, self.kd)
+        if owns_cache:
+            slot = group.slot_map.long()
+            paged.keys[slot // ps, 0, slot % ps] = (xf @ self.wk.T).to(paged.keys.dtype)
+            paged.values[slot // ps, 0, slot % ps] = (xf @ self.wv.T).to(paged.values.dtype)
+        out = torch.empty((T, self.nh * self.vd), dtype=torch.float32, device=x.device)
+        cu, ctx = batch.host.cu_q, batch.host.ctx_len
+        for r in range(batch.num_requests):
+            t0, t1, c = int(cu[r]), int(cu[r + 1]), int(ctx[r])
+            n = c + (t1 - t0)
+            pos = torch.arange(n, device=x.device)
+            pages = group.block_table[r, pos // ps].long()
+            k = paged.keys[pages, 0, pos % ps].float()              # [n, kd]
+            v = paged.values[pages, 0, pos % ps].float()            # [n, vd]
+            scores = torch.einsum("thd,nd->thn", q[t0:t1], k) * self.kd ** -0.5
+            seen = pos.unsqueeze(0) <= (c + torch.arange(t1 - t0, device=x.device)).unsqueeze(1)
+            scores = scores.masked_fill(~seen.unsqueeze(1), float("-inf"))
+            out[t0:t1] = torch.einsum("thn,nv->thv", torch.softmax(scores, -1), v).reshape(t1 - t0, -1)
+        y = out @ self.wo.T
+        if self.bo is not None:
+            y = y + self.bo
+        return y.to(x.dtype)
+
+    @staticmethod
+    def plain(x, wq, wk, wv, wo, bo, nh):
+        T = x.shape[0]
+        kd, vd = wk.shape[0], wv.shape[0]
+        q, k, v = (x @ wq.T).view(T, nh, kd), x @ wk.T, x @ wv.T
+        scores = torch.einsum("thd,nd->thn", q, k) * kd ** -0.5
+        mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
+        p = torch.softmax(scores.masked_fill(~mask.unsqueeze(1), float("-inf")), -1)
+        y = torch.einsum("thn,nv->thv", p, v).reshape(T, nh * vd) @ wo.T
+        return y if bo is None else y + bo
+
+
+class ToyPositionEmbedding:
+    """x_t = E[token_t] + P[position_t]: needs the batch's positions as well as its token ids."""
+
+    @staticmethod
+    def declare(params):
+        n = names_of(params)
+        v, h, m = int(params["vocab_size"]), int(params["hidden_size"]), int(params["max_positions"])
+        return [TensorDecl(n["weight"], (v, h)), TensorDecl(n["positions"], (m, h))]
+
+    def __init__(self, params, tensors, ctx):
+        n = names_of(params)
+        self.table, self.rows = tensors[n["weight"]].float(), tensors[n["positions"]].float()
+
+    def forward(self, batch):
+        return (self.table[batch.token_ids.long()] + self.rows[batch.positions.long()]).contiguous()
+
+
+class ToySandwichBlock:
+    """x = x + norm_b(mixer(norm_a(x)));  x = x + norm_d(feed_forward(norm_c(x))): four norms.
+    A part's output is normalised through the norm interface itself, over a zero stream."""
+
+    def __init__(self, mixer, feed_forward, norms):
+        assert set(norms) == {"pre_mixer", "post_mixer", "pre_feed_forward", "post_feed_forward"}
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+
+    def forward(self, residual, pending, batch, cache, owns_cache):
+        h = self.norms["pre_mixer"].forward(residual, pending)
+        a = self.mixer.forward(h, batch, cache, owns_cache)
+        a = self.norms["post_mixer"].forward(torch.zeros_like(residual), a)
+        h = self.norms["pre_feed_forward"].forward(residual, a)
+        f = self.feed_forward.forward(h, batch)
+        return self.norms["post_feed_forward"].forward(torch.zeros_like(residual), f)
+
+
+class ToyMixerOnlyBlock:
+    """x = x + mixer(norm(x)): a layer without a feed-forward."""
+
+    def __init__(self, mixer, feed_forward, norms):
+        assert feed_forward is None and set(norms) == {"mixer"}
+        self.mixer, self.feed_forward, self.norm = mixer, None, norms["mixer"]
+
+    def forward(self, residual, pending, batch, cache, owns_cache):
+        return self.mixer.forward(self.norm.forward(residual, pending), batch, cache, owns_cache)
+
+
 def register_toys():
     MIXERS.register("toy_decay", ToyDecayMixer)
+    MIXERS.register("toy_wide_value", ToyWideValueMixer)
     FEED_FORWARDS.register("toy_routed", ToyRoutedFF)
     POSITION_ENCODINGS.register("toy_shift", ToyShiftEncoding)
+    EMBEDDINGS.register("toy_position_embedding", ToyPositionEmbedding)
+    ARRANGEMENTS.register("toy_sandwich", ToySandwichBlock)
+    ARRANGEMENTS.register("toy_mixer_only", ToyMixerOnlyBlock)
 
 
 def unregister_toys():
     MIXERS.unregister("toy_decay")
+    MIXERS.unregister("toy_wide_value")
     FEED_FORWARDS.unregister("toy_routed")
     POSITION_ENCODINGS.unregister("toy_shift")
+    EMBEDDINGS.unregister("toy_position_embedding")
+    ARRANGEMENTS.unregister("toy_sandwich")
+    ARRANGEMENTS.unregister("toy_mixer_only")
