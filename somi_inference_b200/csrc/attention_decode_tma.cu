@@ -77,7 +77,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     const int split = blockIdx.x, kvh = blockIdx.y, i = blockIdx.z;
     const int req = req_base + i, row = row_base + i;
     const int G = nq / nkv;
-    const TdRange rg = td_range(ctx_len[req], window);
+    const TdRange rg = td_range(ld_step(ctx_len + req), window);      // before the wait
     if (split < rg.first_split || split >= rg.n_splits) {
         pdl_wait();
         return;
@@ -110,7 +110,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
         for (int p = lane; p < pages_in_chunk; p += 32) {
             const int ap = chunk_page0 + p;
             if (ap < first_page || ap > last_page || ap == newest_page) continue;
-            const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
+            const long long prow = (static_cast<long long>(ld_step(bt + ap)) * nkv + kvh) * page_size;
             const int r = p * page_size;
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
@@ -135,7 +135,7 @@ paged_decode_tma_kernel(const __grid_constant__ CUtensorMap kv_map,
     if (warp == 0 && newest_page >= max(first_page, chunk_page0) &&
         newest_page <= last_page && lane == (newest_page - chunk_page0) % 32) {
         const int p = newest_page - chunk_page0;
-        const long long prow = (static_cast<long long>(bt[newest_page]) * nkv + kvh) * page_size;
+        const long long prow = (static_cast<long long>(ld_step(bt + newest_page)) * nkv + kvh) * page_size;
         const int r = p * page_size;
 #pragma unroll
         for (int h = 0; h < HALVES; ++h)
@@ -327,7 +327,7 @@ paged_decode_ring_kernel(const __grid_constant__ CUtensorMap kv_map,
     const int group = blockIdx.x, kvh = blockIdx.y, i = blockIdx.z;
     const int req = req_base + i, row = row_base + i;
     const int G = nq / nkv;
-    const TdRange rg = td_range(ctx_len[req], window);
+    const TdRange rg = td_range(ld_step(ctx_len + req), window);      // before the wait
     const int c_begin = max(group * cpc, rg.first_split);
     const int c_end = min((group + 1) * cpc, rg.n_splits);
     if (c_begin >= c_end) {
@@ -399,7 +399,7 @@ paged_decode_ring_kernel(const __grid_constant__ CUtensorMap kv_map,
             const bool mine = lane < pages_in_chunk && ap >= fp && ap <= lp;
             const bool has_newest = newest_page >= fp && newest_page <= lp;
             auto copy = [&]() {
-                const long long prow = (static_cast<long long>(bt[ap]) * nkv + kvh) * page_size;
+                const long long prow = (static_cast<long long>(ld_step(bt + ap)) * nkv + kvh) * page_size;
                 unsigned char* dst = tiles + st * TILE + lane * page_size * 128;
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h)

@@ -95,6 +95,16 @@ inline int launch_status() { return static_cast<int>(cudaGetLastError()); }
 //                full barrier in the stream.
 // Outputs of ANY kernel of the same step (not only the direct predecessor's) are off limits
 // before the wait.  Reads before a wait are tagged with one of the three classes above.
+//
+// What changes from step to step at fixed addresses ([descriptor], and the tables that lead to
+// [old-cache]) is read with `ld_step` before the wait: `ld.global.cg`, served from L2, where the
+// copy of the descriptor arrived before the step's first kernel started.  A plain load of a
+// `const __restrict__` pointer may go through the SM's read-only cache, whose contents are only
+// defined for data that nobody writes during the kernel's lifetime; a kernel that starts before
+// its predecessor has ended stretches that lifetime, so these few loads take the path whose
+// coherence does not depend on it.  After the wait plain loads are used.  Bulk tensor copies
+// (TMA) read through L2 as well.
+__device__ __forceinline__ int ld_step(const int* p) { return __ldcg(p); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");

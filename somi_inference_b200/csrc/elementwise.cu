@@ -149,14 +149,14 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     // the step: the angles are ready when the projection is
     const int t = blockIdx.x;
     const int half = rot >> 1;
-    const float pos = static_cast<float>(positions[t]);
+    const float pos = static_cast<float>(ld_step(positions + t));
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float s, c;
         sincosf(pos * inv_freq[i], &s, &c);
         cs[i] = c;
         cs[half + i] = s;
     }
-    const int slot = slot_map ? slot_map[t] : -1;
+    const int slot = slot_map ? ld_step(slot_map + t) : -1;
     pdl_wait();
     __syncthreads();
     T* row = qkv + static_cast<size_t>(t) * (nq + 2 * nkv) * hd;
@@ -258,11 +258,11 @@ rope_store_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict_
     for (int idx = threadIdx.x; idx < n_tok * half; idx += blockDim.x) {
         const int tt = idx / half, i = idx - tt * half;
         float sn, c;
-        sincosf(static_cast<float>(positions[t0 + tt]) * inv_freq[i], &sn, &c);
+        sincosf(static_cast<float>(ld_step(positions + t0 + tt)) * inv_freq[i], &sn, &c);
         cs[tt * rot + i] = c;
         cs[tt * rot + half + i] = sn;
     }
-    if (threadIdx.x < n_tok) slot_s[threadIdx.x] = slot_map ? slot_map[t0 + threadIdx.x] : -1;
+    if (threadIdx.x < n_tok) slot_s[threadIdx.x] = slot_map ? ld_step(slot_map + t0 + threadIdx.x) : -1;
     pdl_wait();
     __syncthreads();
     const int width = (nq + 2 * nkv) * hd;
@@ -333,14 +333,14 @@ __global__ void rope_store_partial_kernel(const float* __restrict__ parts, int s
     const int t = blockIdx.x;
     const int half = rot >> 1;
     const int width = (nq + 2 * nkv) * hd;
-    const float pos = static_cast<float>(positions[t]);
+    const float pos = static_cast<float>(ld_step(positions + t));
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float s, c;
         sincosf(pos * inv_freq[i], &s, &c);
         cs[i] = c;
         cs[half + i] = s;
     }
-    const int slot = slot_map ? slot_map[t] : -1;
+    const int slot = slot_map ? ld_step(slot_map + t) : -1;
     pdl_wait();             // the partial sums (and the bias add) come after it
     __syncthreads();
     const float* prow = parts + static_cast<size_t>(t) * width;

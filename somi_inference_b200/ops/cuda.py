@@ -479,6 +479,23 @@ class CudaOps:
                        2.0 * M * N * K, detail=f"M={M} N={N} K={K} mode={mode}")
         return out
 
+    def gemm_f32(self, x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+        """x[M, K] @ w[N, K]^T (+ bias) in float32 FMAs, each output summed over K in ascending
+        order (the float32 path's product; the library's is not used there)."""
+        _check(x, w, bias)
+        M, K = x.shape
+        N = w.shape[0]
+        if not (x.dtype == w.dtype == torch.float32 and w.shape[1] == K
+                and (bias is None or (bias.dtype == torch.float32 and bias.numel() == N))):
+            raise KernelError("gemm_f32 takes float32 x[M, K], w[N, K] and bias[N]")
+        out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        rc = self.lib.somi_gemm_f32(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), ctypes.c_int(M),
+                                    ctypes.c_int(N), ctypes.c_int(K), self._stream())
+        self._done(rc, "gemm_f32")
+        if trace.active():
+            trace.note("gemm_f32", (N * K + M * K + M * N) * 4, 2.0 * M * N * K, detail=f"M={M} N={N} K={K}")
+        return out
+
     def sample(self, logits, temperature, top_k, top_p, penalty, seed, counter, hist_off,
                hist_tok, out) -> None:
         """seed: int32 view of uint64 pairs [2 * rows]; counter: int32 view of uint32 [rows]."""

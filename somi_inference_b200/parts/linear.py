@@ -4,9 +4,9 @@ The reference's engine uses `nn.Linear` for every projection
 (somi_inference/models/qwen2.py:221-222,268-271), i.e. the library GEMM.  Here a step with few
 tokens (bfloat16, at most `ops.skinny_max_tokens` rows) runs the engine's own tcgen05 kernel,
 which streams the weight once through TMA and tensor memory and can leave split-K partial sums
-or apply SiLU(gate)*up in its epilogue; everything else (prompt portions, float32) goes to the
-library product.  In float32 that product is a true 32-bit one: the reduced-precision matrix
-mode (TF32) is switched off process-wide when the package is imported.
+or apply SiLU(gate)*up in its epilogue; larger bfloat16 steps (prompt portions) go to the library
+product.  float32 goes to the engine's own float32 kernel (`csrc/gemm_f32.cu`: plain FMAs, every
+output summed over K in ascending order whatever the step's size), not to the library.
 """
 
 from __future__ import annotations
@@ -29,9 +29,15 @@ class Linear:
         return (ops is not None and x.is_cuda and getattr(ops, "skinny_supported", None) is not None
                 and ops.skinny_supported(x.shape[0], self.out_features, self.in_features, x.dtype))
 
+    def own_f32(self, x: torch.Tensor) -> bool:
+        return (x.dtype == torch.float32 and x.is_cuda and self.weight.dtype == torch.float32
+                and getattr(self.ops, "gemm_f32", None) is not None)
+
     def __call__(self, x: torch.Tensor) -> torch.Tensor:
         if self.skinny(x):
             return self.ops.skinny_gemm(x, self.weight, self.bias, self.ops.GEMM_BF16)
+        if self.own_f32(x):
+            return self.ops.gemm_f32(x, self.weight, self.bias)
         y = F.linear(x, self.weight, self.bias)
         self._note(x, y)
         return y
@@ -62,6 +68,8 @@ class Linear:
         """x W^T with a float32 result (accumulation is float32 in every path)."""
         if self.skinny(x):
             return self.ops.skinny_gemm(x, self.weight, None, self.ops.GEMM_F32)
+        if self.own_f32(x):
+            return self.ops.gemm_f32(x, self.weight, None)
         if x.dtype == torch.float32:
             y = F.linear(x, self.weight)
         elif _MM_TAKES_OUT_DTYPE:

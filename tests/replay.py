@@ -115,17 +115,26 @@ def mixed(requests: dict[str, list[int]], seed: int = 0, live: int = 4,
     return steps, peak
 
 
+LAST_RUN: dict = {}      # (request, position) -> (step, tokens in the step, replayed from a graph?)
+
+
 def run_steps(engine, steps: list[dict]) -> dict[tuple[str, int], torch.Tensor]:
     out: dict[tuple[str, int], torch.Tensor] = {}
     fed: dict[str, int] = {}
+    LAST_RUN.clear()
     for rec in steps:
         entries = [StepEntry(e["id"], e["tokens"], e["want"]) for e in rec["entries"]]
+        graphs = getattr(engine, "_graphs", None)
+        hits = graphs.hits if graphs is not None else 0
         logits = engine.step(entries).float().cpu()
+        replayed = graphs is not None and graphs.hits > hits
         k = 0
         for e in rec["entries"]:
             base = fed.get(e["id"], 0)
             for w in e["want"]:
                 out[(e["id"], base + w)] = logits[k]
+                LAST_RUN[(e["id"], base + w)] = (rec["step"], [len(x["tokens"]) for x in rec["entries"]],
+                                                 replayed)
                 k += 1
             fed[e["id"]] = base + len(e["tokens"])
         assert k == logits.shape[0]
@@ -186,14 +195,20 @@ def compare(got: dict, reference: dict[str, torch.Tensor], atol: float, what: st
     worst = 0.0
     where = None
     sq, n = 0.0, 0
+    off = []
     for (rid, pos), row in got.items():
         diff = row.double() - reference[rid][pos].double()
         err = diff.abs().max().item()
         sq += float(diff.pow(2).sum())
         n += diff.numel()
+        if not err <= atol:
+            off.append((rid, pos, float(f"{err:.3g}")))
         if not err <= worst:      # also catches NaN
             worst, where = err, (rid, pos)
-    assert worst <= atol, f"{what}: worst error {worst:.3e} at request/position {where} (allowed {atol:.1e})"
+    assert worst <= atol, (f"{what}: worst error {worst:.3e} at request/position {where} (allowed "
+                           f"{atol:.1e}); {len(off)} rows off, the first: {off[:12]}; their steps "
+                           f"(step, tokens of its entries, replayed from a graph): "
+                           f"{[LAST_RUN.get((r, p)) for r, p, _ in off[:12]]}")
     if rms_tol is not None:
         rms = (sq / max(n, 1)) ** 0.5
         assert rms <= rms_tol, f"{what}: rms error {rms:.3e} (allowed {rms_tol:.1e})"

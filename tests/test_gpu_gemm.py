@@ -24,7 +24,7 @@ def test_skinny_gemm_bf16_and_f32(ops, M, N, K):
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
     b = torch.randn(N, generator=g).to(torch.bfloat16).cuda()
-    ref = x.float() @ w.float().T
+    ref = (x.double() @ w.double().T).float()       # float64: no doubt about the reference
     y32 = ops.skinny_gemm(x, w, None, ops.GEMM_F32)
     ops.check_errors()
     scale = ref.abs().max().item()
@@ -44,7 +44,7 @@ def test_skinny_gemm_split_k(ops, M, N, K, splits):
     parts = ops.skinny_gemm(x, w, b, ops.GEMM_PARTIAL_F32, splits=splits)
     ops.check_errors()
     assert 1 <= parts.shape[0] <= splits
-    ref = x.float() @ w.float().T + b
+    ref = (x.double() @ w.double().T + b.double()).float()
     assert (parts.sum(0) - ref).abs().max().item() <= 1e-4 * max(ref.abs().max().item(), 1.0)
 
 
@@ -57,7 +57,7 @@ def test_skinny_gemm_swiglu(ops, M, I, K):
     w = torch.stack([gate, up], dim=1).reshape(2 * I, K).contiguous()     # rows g0, u0, g1, u1, ...
     y = ops.skinny_gemm(x, w, None, ops.GEMM_SWIGLU)
     ops.check_errors()
-    gg, uu = x.float() @ gate.float().T, x.float() @ up.float().T
+    gg, uu = (x.double() @ gate.double().T).float(), (x.double() @ up.double().T).float()
     ref = gg * torch.sigmoid(gg) * uu
     torch.testing.assert_close(y.float(), ref, rtol=1.6e-2, atol=1e-2 * max(ref.abs().max().item(), 1.0))
 
@@ -71,7 +71,7 @@ def test_skinny_gemm_launched_alone_many_times(ops, M, N, K):
     g = torch.Generator().manual_seed(5)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
-    ref = x.float() @ w.float().T
+    ref = (x.double() @ w.double().T).float()
     scale = max(ref.abs().max().item(), 1.0)
     first = None
     for i in range(40):
@@ -84,3 +84,34 @@ def test_skinny_gemm_launched_alone_many_times(ops, M, N, K):
         else:
             assert torch.equal(y, first), f"launch {i} differs from the first"
     ops.check_errors()
+
+
+@pytest.mark.parametrize("M", [1, 2, 5, 16, 17, 32, 33, 100, 300])
+@pytest.mark.parametrize("N,K", [(320, 192), (640, 192), (384, 80), (517, 80), (80, 176), (1000, 192),
+                                 (4608, 3584), (896, 4864), (7, 3), (129, 1025)])
+def test_float32_product(ops, M, N, K):
+    """The float32 path's own product against a float64 product, with and without bias, at the
+    tiny models' sizes, at large ones and at sizes that are no multiple of anything."""
+    g = torch.Generator().manual_seed(N * 7 + K + M)
+    x = torch.randn(M, K, generator=g).cuda()
+    w = (torch.randn(N, K, generator=g) * 0.1).cuda()
+    b = torch.randn(N, generator=g).cuda()
+    ref = x.double() @ w.double().T
+    tol = 2e-6 * float(ref.abs().max()) * max(1.0, (K / 64) ** 0.5)
+    y = ops.gemm_f32(x, w)
+    assert (y.double() - ref).abs().max().item() <= tol
+    yb = ops.gemm_f32(x, w, b)
+    assert (yb.double() - (ref + b.double())).abs().max().item() <= tol + 1e-6
+
+
+def test_float32_product_does_not_depend_on_the_other_rows(ops):
+    """An output element is the sum of its K terms in ascending order whatever the step's size:
+    the same row gives the same bits alone, among 30 rows and among 300."""
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(300, 896, generator=g).cuda()
+    w = (torch.randn(1152, 896, generator=g) * 0.1).cuda()
+    b = torch.randn(1152, generator=g).cuda()
+    whole = ops.gemm_f32(x, w, b)
+    assert torch.equal(ops.gemm_f32(x[:30].contiguous(), w, b), whole[:30])
+    for r in (0, 17, 299):
+        assert torch.equal(ops.gemm_f32(x[r:r + 1].contiguous(), w, b), whole[r:r + 1])

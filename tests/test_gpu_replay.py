@@ -93,3 +93,64 @@ def test_cut_independence_float32(models):
     for key in outs[0]:
         for o in outs[1:]:
             assert (outs[0][key] - o[key]).abs().max().item() < 1e-5
+
+
+def test_cut_independence_bfloat16(models):
+    """In bfloat16 the bits of a cached key depend on the product that made it: a step of few
+    tokens sums the projection in float32 and rounds once, after the rotation; a larger step takes
+    the library's product, which rounds to bfloat16 before the rotation rounds again.  So the same
+    position computed whole, token by token (as after a preemption that recomputes) or in portions
+    differs, but by rounding only: directly compared, within the bounds that each cut keeps against
+    the plain implementation."""
+    from somi_inference_b200.engine import Engine
+    d, cfg, reqs, ref, scale = models[("D", torch.bfloat16)]
+    sub = {"r2": reqs["r2"]}
+    outs = []
+    for mode in ("whole", "last32", "portions"):
+        steps, mt = MODES[mode](sub)
+        eng = Engine(d, dtype="bfloat16", page_size=16, max_tokens=mt)
+        outs.append(replay.run_steps(eng, steps))
+    for o in outs[1:]:
+        diff = torch.stack([outs[0][k] - o[k] for k in outs[0]])
+        assert diff.abs().max().item() <= 4e-2 * scale
+        assert diff.pow(2).mean().sqrt().item() <= 4e-3 * scale
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "D"])
+def test_steps_replayed_from_graphs_match_plain(models, name, dtype):
+    """A step whose layout has been seen twice is captured in a CUDA graph and replayed from then
+    on.  One prompt-portion layout (16 tokens of one request) and one decode layout (two requests,
+    one token each) are fed many times, with different tokens, cached lengths and pages; the
+    replayed steps must give the plain logits like any other."""
+    from somi_inference_b200.engine import Engine, StepEntry
+    d, cfg, reqs, ref, scale = models[(name, getattr(torch, dtype))]
+    ids = list(reqs)[:4]
+    portion = 16
+    eng = Engine(d, dtype=dtype, page_size=PAGE_SIZES[name],
+                 max_tokens=2 * max(replay.round_up(len(reqs[r]), 64) for r in ids))
+    got = {}
+    for pair in (ids[:2], ids[2:]):
+        fed = {r: 0 for r in pair}
+        # the prompts, in portions of 16 (the tail, shorter than that, in one step of its own)
+        for r in pair:
+            head = (len(reqs[r]) - 8) // portion * portion
+            while fed[r] < head:
+                toks = reqs[r][fed[r]:fed[r] + portion]
+                logits = eng.step([StepEntry(r, toks, [0, portion - 1])]).float().cpu()
+                got[(r, fed[r])], got[(r, fed[r] + portion - 1)] = logits[0], logits[1]
+                fed[r] += portion
+        # both requests decode together while both have tokens left: one layout, many steps
+        while all(fed[r] < len(reqs[r]) for r in pair):
+            logits = eng.step([StepEntry(r, [reqs[r][fed[r]]], [0]) for r in pair]).float().cpu()
+            for k, r in enumerate(pair):
+                got[(r, fed[r])] = logits[k]
+                fed[r] += 1
+        for r in pair:
+            eng.end(r)                      # the next pair gets these pages
+        eng.cache.check_consistency()
+    graphs = eng._graphs
+    assert len(graphs) >= 2, "the portion layout and the decode layout should both be captured"
+    assert graphs.hits >= 12, f"only {graphs.hits} steps were replayed"
+    eng.ops.check_errors()
+    replay.compare(got, ref, ATOL[dtype](scale), f"graphs {name}/{dtype}", RMS[dtype](scale))

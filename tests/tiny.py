@@ -43,7 +43,7 @@ PAGE_SIZES = {"A": 16, "B": 8, "C": 16, "D": 16}
 
 
 def make_model(name: str, root: str, dtype=torch.float32, std: float = 0.02) -> str:
-    out = os.path.join(root, f"tiny_{name}_{str(dtype).split('.')[-1]}")
+    out = os.path.join(root, f"tiny_{name}_{str(dtype).split('.')[-1]}_std{std}")
     if not os.path.isdir(out):
         write_random_model(Qwen2Config.from_dict(TINY[name]), SEEDS[name], out, dtype=dtype, std=std)
     return out

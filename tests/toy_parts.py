@@ -20,6 +20,15 @@ from __future__ import annotations
 
 import torch
 
+
+def mm(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a[..., K] times b[N, K] transposed, written as a product and a sum: the toy parts' sizes
+    are tiny, and on the GPU this keeps them off the library's float32 matrix product (whose
+    results the engine's own float32 path deliberately does not rely on)."""
+    if not a.is_cuda:
+        return a @ b.T
+    return (a.unsqueeze(-2) * b).sum(-1)
+
 from somi_inference_b200.parts import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, MIXERS,
                                        POSITION_ENCODINGS)
 from somi_inference_b200.parts.base import (CacheNeeds, PagedKVNeeds, StateNeeds, TensorDecl,
@@ -44,7 +53,7 @@ class ToyDecayMixer:
 
     def forward(self, x, batch, cache, owns_cache):
         state = cache.state["s"]
-        u = x.float() @ self.w_in.T
+        u = mm(x.float(), self.w_in)
         out = torch.empty_like(u)
         cu = batch.host.cu_q
         for r, slot in enumerate(batch.host.state_slot.tolist()):
@@ -54,7 +63,7 @@ class ToyDecayMixer:
                 out[t] = s
             if owns_cache:
                 state[slot] = s
-        return (out @ self.w_out.T).to(x.dtype)
+        return mm(out, self.w_out).to(x.dtype)
 
     @staticmethod
     def plain(x, w_in, w_out, decay):
@@ -86,11 +95,11 @@ class ToyRoutedFF:
 
     @staticmethod
     def plain(x, router, w1, w2):
-        choice = torch.argmax(x @ router.T, dim=-1)
+        choice = torch.argmax(mm(x, router), dim=-1)
         out = torch.empty_like(x)
         for t in range(x.shape[0]):
             e = int(choice[t])
-            out[t] = torch.relu(x[t] @ w1[e].T) @ w2[e].T
+            out[t] = mm(torch.relu(mm(x[t], w1[e])), w2[e])
         return out
 
 
@@ -149,11 +158,11 @@ class ToyWideValueMixer:
         ps = paged.page_size
         xf = x.float()
         T = xf.shape[0]
-        q = (xf @ self.wq.T).view(T, self.nh, self.kd)
+        q = mm(xf, self.wq).view(T, self.nh, self.kd)
         if owns_cache:
             slot = group.slot_map.long()
-            paged.keys[slot // ps, 0, slot % ps] = (xf @ self.wk.T).to(paged.keys.dtype)
-            paged.values[slot // ps, 0, slot % ps] = (xf @ self.wv.T).to(paged.values.dtype)
+            paged.keys[slot // ps, 0, slot % ps] = mm(xf, self.wk).to(paged.keys.dtype)
+            paged.values[slot // ps, 0, slot % ps] = mm(xf, self.wv).to(paged.values.dtype)
         out = torch.empty((T, self.nh * self.vd), dtype=torch.float32, device=x.device)
         cu, ctx = batch.host.cu_q, batch.host.ctx_len
         for r in range(batch.num_requests):
@@ -163,11 +172,12 @@ class ToyWideValueMixer:
             pages = group.block_table[r, pos // ps].long()
             k = paged.keys[pages, 0, pos % ps].float()              # [n, kd]
             v = paged.values[pages, 0, pos % ps].float()            # [n, vd]
-            scores = torch.einsum("thd,nd->thn", q[t0:t1], k) * self.kd ** -0.5
+            scores = (q[t0:t1].unsqueeze(2) * k).sum(-1) * self.kd ** -0.5          # [t, h, n]
             seen = pos.unsqueeze(0) <= (c + torch.arange(t1 - t0, device=x.device)).unsqueeze(1)
             scores = scores.masked_fill(~seen.unsqueeze(1), float("-inf"))
-            out[t0:t1] = torch.einsum("thn,nv->thv", torch.softmax(scores, -1), v).reshape(t1 - t0, -1)
-        y = out @ self.wo.T
+            probs = torch.softmax(scores, -1)
+            out[t0:t1] = (probs.unsqueeze(-1) * v).sum(2).reshape(t1 - t0, -1)         # [t, h, v]
+        y = mm(out, self.wo)
         if self.bo is not None:
             y = y + self.bo
         return y.to(x.dtype)
