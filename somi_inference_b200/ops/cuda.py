@@ -63,7 +63,12 @@ class CudaOps:
         self.prefill_q_tile = int(self.lib.somi_prefill_q_tile())
         self.lib.somi_prefill_tc_q_tile.restype = ctypes.c_int
         self.prefill_tc_q_tile = int(self.lib.somi_prefill_tc_q_tile())
-        self.q_tile_sizes = (self.generic_q_tile, self.prefill_q_tile, self.prefill_tc_q_tile)
+        self.lib.somi_prefill_pp_q_tile.restype = ctypes.c_int
+        self.prefill_pp_q_tile = int(self.lib.somi_prefill_pp_q_tile())
+        self.q_tile_sizes = (self.generic_q_tile, self.prefill_q_tile, self.prefill_tc_q_tile,
+                             self.prefill_pp_q_tile)
+        self.use_pp_prefill = True
+        self.pp_prefill_min_ctas = torch.cuda.get_device_properties(0).multi_processor_count
         self.use_tc_prefill = True
         self._q_maps: dict = {}
         self.lib.somi_decode_chunk.restype = ctypes.c_int
@@ -245,6 +250,9 @@ class CudaOps:
         if int(self.lib.somi_prefill_tma_error()) != 0:
             raise KernelError("the TMA prefill attention kernel gave up waiting for a copy; "
                               "its results are not valid")
+        if int(self.lib.somi_prefill_pp_error()) != 0:
+            raise KernelError("the two-tile tcgen05 prefill attention kernel gave up waiting on a "
+                              "barrier; its results are not valid")
         if int(self.lib.somi_prefill_tc_error()) != 0:
             raise KernelError("the tcgen05 prefill attention kernel gave up waiting on a barrier; "
                               "its results are not valid")
@@ -288,13 +296,30 @@ class CudaOps:
         tensor_core_prefill = (batch.num_prefill_requests > 0
                                and self.prefill_supported(nq, nkv, hd, qkv.dtype))
         if tensor_core_prefill:
-            # Three kernels, the first that takes the sizes: both products on tcgen05 with
-            # accumulators in tensor memory (measured on 2,048-token prompts: 60 vs 160 us per
-            # 7B-shaped layer, 25 vs 67 us per 0.5B-shaped layer), mma.sync fed by TMA, mma.sync
-            # fed by cp.async gathers.
+            # Four kernels, the first that takes the sizes: both products on tcgen05 with
+            # accumulators in tensor memory, two query tiles per CTA in ping-pong and the
+            # probabilities handed on through tensor memory; the same with one query tile per CTA
+            # and the probabilities through shared memory; mma.sync fed by TMA; mma.sync fed by
+            # cp.async gathers.
             sizes = (ctypes.c_int(nq), ctypes.c_int(nkv), ctypes.c_int(hd), ctypes.c_int(page_size))
             row_bytes = hd * 2
-            if (self.use_tc_prefill and storage is not None and qkv.shape[1] % 8 == 0
+            # (the two-tile kernel has half as many CTAs: below one per SM the one-tile kernel,
+            # with twice as many, is the faster: 0.5B shape at 2,048 tokens 123 vs 148 TFLOP/s)
+            if (self.use_pp_prefill and storage is not None and qkv.shape[1] % 8 == 0
+                    and batch.tiles[self.prefill_pp_q_tile].shape[0] * nq >= self.pp_prefill_min_ctas
+                    and bool(self.lib.somi_prefill_pp_supported(*sizes))):
+                tiles = batch.tiles[self.prefill_pp_q_tile]
+                rc = self.lib.somi_paged_attention_prefill_pp(
+                    ctypes.c_void_p(self._q_tensor_map(qkv)),
+                    ctypes.c_void_p(self._kv_tensor_map(storage, hd, page_size)),
+                    ctypes.c_longlong((kcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    ctypes.c_longlong((vcache.data_ptr() - storage.data_ptr()) // row_bytes),
+                    _ptr(group.block_table), ctypes.c_int(group.width), _ptr(batch.cu_q),
+                    _ptr(batch.ctx_len), _ptr(tiles), ctypes.c_int(tiles.shape[0]), *sizes,
+                    ctypes.c_float(scale), ctypes.c_int(win), _ptr(out), self._stream())
+                self._done(rc, "paged_attention_prefill_pp")
+                kernel = "attention_prefill_tcgen05_pingpong"
+            elif (self.use_tc_prefill and storage is not None and qkv.shape[1] % 8 == 0
                     and bool(self.lib.somi_prefill_tc_supported(*sizes))):
                 tiles = batch.tiles[self.prefill_tc_q_tile]
                 rc = self.lib.somi_paged_attention_prefill_tc(

@@ -177,10 +177,20 @@ def test_attention_far_key_and_window_edge(ops, dtype, window):
         assert close == seen, f"key at {spot}: seen={seen}, output equals its value: {close}"
 
 
+@pytest.fixture(params=["pingpong", "tcgen05"])
+def prefill_kernel(request, ops):
+    """Run a prompt-attention test on the two-tile tcgen05 kernel (whatever the step's size) or on
+    the one-tile kernel."""
+    was = ops.use_pp_prefill, ops.pp_prefill_min_ctas
+    ops.use_pp_prefill, ops.pp_prefill_min_ctas = request.param == "pingpong", 0
+    yield request.param
+    ops.use_pp_prefill, ops.pp_prefill_min_ctas = was
+
+
 @pytest.mark.parametrize("window", [None, 130])
 @pytest.mark.parametrize("nq,nkv,hd", [(4, 2, 128), (6, 2, 64)])
-def test_prefill_attention_far_key_and_window_edge(ops, nq, nkv, hd, window):
-    """The same for a prompt portion (the tcgen05 kernel): one key is made to dominate for one
+def test_prefill_attention_far_key_and_window_edge(ops, prefill_kernel, nq, nkv, hd, window):
+    """The same for a prompt portion (the tcgen05 kernels): one key is made to dominate for one
     query row; that row's output must be the key's value, or must not see it.  Rows at the first
     and last position of the portion and on both sides of a 128-row tile edge; keys far back, on
     both sides of the 128-key tile edges, in the first and last slot of a page, on the diagonal,
@@ -290,7 +300,7 @@ PREFILL_CASES = [
 ]
 
 
-@pytest.mark.parametrize("path", ["tcgen05", "tma", "cp_async"])
+@pytest.mark.parametrize("path", ["pingpong", "tcgen05", "tma", "cp_async"])
 @pytest.mark.parametrize("case", PREFILL_CASES, ids=[f"p{i}" for i in range(len(PREFILL_CASES))])
 def test_tensor_core_prefill_attention(ops, case, path):
     """Portions with and without cached context, around the 64-row and 64-key tile edges,
@@ -301,6 +311,8 @@ def test_tensor_core_prefill_attention(ops, case, path):
                                               window=window, requests=reqs, dtype=torch.bfloat16,
                                               seed=11)
     out = torch.full((batch.num_tokens, nq * hd), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.use_pp_prefill = path == "pingpong"
+    ops.pp_prefill_min_ctas, min_ctas = 0, ops.pp_prefill_min_ctas     # the tests' steps are small
     ops.use_tc_prefill = path == "tcgen05"
     ops.use_tma_prefill = path != "cp_async"
     try:
@@ -308,7 +320,8 @@ def test_tensor_core_prefill_attention(ops, case, path):
                             hd ** -0.5, window, out, storage=view.storage)
         ops.check_errors()
     finally:
-        ops.use_tma_prefill = ops.use_tc_prefill = True
+        ops.use_tma_prefill = ops.use_tc_prefill = ops.use_pp_prefill = True
+        ops.pp_prefill_min_ctas = min_ctas
     ref = torch.empty(batch.num_tokens, nq * hd, dtype=torch.bfloat16)
     cb = batch_to_cpu(batch)
     HOST.paged_attention(qkv.cpu(), view.keys.cpu(), view.values.cpu(), cb, cb.groups[0], nq, nkv,
