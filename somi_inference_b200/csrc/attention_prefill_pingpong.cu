@@ -207,18 +207,16 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
             if (ok) t5::commit(smem_u32(&k_empty[0]));
             for (int t = 0; t < n_t && ok; ++t) {
                 const int st = t % STAGES;
-                bool next_keys_ready = false;
+                // the tiles this iteration reads arrived long ago: their barriers are tested
+                // before the wait for the probabilities, so that no test (a couple of hundred
+                // cycles even on a completed barrier) sits between the products of a query tile
                 wait(&v_full[st], (t / STAGES) & 1);
+                if (t + 1 < n_t) wait(&k_full[(t + 1) % STAGES], ((t + 1) / STAGES) & 1);
                 if (t < n_a) {
                     wait(&p_full[0], t & 1);
                     if (!ok) break;
                     outputs(0, t);
-                    if (t + 1 < n_a) {
-                        wait(&k_full[(t + 1) % STAGES], ((t + 1) / STAGES) & 1);
-                        if (!ok) break;
-                        next_keys_ready = true;
-                        scores(0, t + 1);
-                    }
+                    if (t + 1 < n_a) scores(0, t + 1);
                 }
                 if (has_b) {
                     wait(&p_full[1], t & 1);
@@ -227,11 +225,7 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
                 }
                 t5::commit(smem_u32(&v_empty[st]));
                 if (t + 1 < n_t) {
-                    if (has_b) {
-                        if (!next_keys_ready) wait(&k_full[(t + 1) % STAGES], ((t + 1) / STAGES) & 1);
-                        if (!ok) break;
-                        scores(1, t + 1);
-                    }
+                    if (has_b) scores(1, t + 1);
                     t5::commit(smem_u32(&k_empty[(t + 1) % STAGES]));
                 }
             }

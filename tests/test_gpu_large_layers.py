@@ -180,6 +180,32 @@ def test_portion_of_512_beside_64_single_tokens_against_plain(weights, dtype):
     check_against_plain(got, ref, dtype, f"{name}/{dtype}/512+64")
 
 
+def test_long_prompt_in_two_portions_against_plain(weights):
+    """A prompt of 700 tokens in portions of 400 and 300 through the prompt-attention kernel with
+    two query tiles per CTA (made to take the step whatever its size), bfloat16, against the plain
+    implementation at rows on both sides of the 128- and 256-row tile edges."""
+    from somi_inference_b200.engine import Engine, StepEntry
+    name, cfg, tensors = weights
+    g = torch.Generator().manual_seed(14)
+    prompt = torch.randint(0, cfg.vocab_size, (700,), generator=g).tolist()
+    eng = Engine.from_tensors(cfg, tensors, dtype="bfloat16", page_size=16, max_tokens=768, max_requests=2)
+    was = eng.ops.pp_prefill_min_ctas
+    eng.ops.pp_prefill_min_ctas = 0
+    try:
+        want_a = [0, 127, 128, 255, 256, 399]
+        want_b = [0, 111, 112, 113, 299]           # positions 400, 511, 512, 513, 699
+        la = eng.step([StepEntry("p", prompt[:400], want_a)]).float().cpu()
+        lb = eng.step([StepEntry("p", prompt[400:], want_b)]).float().cpu()
+        eng.ops.check_errors()
+    finally:
+        eng.ops.pp_prefill_min_ctas = was
+    got = {("p", w): la[i] for i, w in enumerate(want_a)}
+    got.update({("p", 400 + w): lb[i] for i, w in enumerate(want_b)})
+    del eng
+    ref = plain_rows(name, cfg, tensors, {"p": prompt}, set(got))
+    check_against_plain(got, ref, "bfloat16", f"{name}/bfloat16/700 tokens in two portions")
+
+
 def test_portion_of_512_beside_64_single_tokens_at_2048_context(weights):
     """The same step at the benchmark's sizes: 64 requests with 2,048 cached tokens and a prompt
     with 1,024 cached tokens; bfloat16 against the engine's float32 path."""

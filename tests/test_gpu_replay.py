@@ -95,6 +95,28 @@ def test_cut_independence_float32(models):
             assert (outs[0][key] - o[key]).abs().max().item() < 1e-5
 
 
+@pytest.mark.parametrize("mode", ["whole", "portions", "mixed"])
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_replay_with_the_two_tile_prompt_attention(models, name, mode):
+    """The prompt-attention kernel with two query tiles per CTA is chosen by itself only for steps
+    with at least a CTA per SM, which no tiny model reaches: here it is made to take every prompt
+    portion (head sizes 64 and 128; whole prompts of several tiles, portions down to two tokens,
+    portions beside single tokens with pages handed on)."""
+    from somi_inference_b200.engine import Engine
+    d, cfg, reqs, ref, scale = models[(name, torch.bfloat16)]
+    steps, max_tokens = MODES[mode](reqs)
+    eng = Engine(d, dtype="bfloat16", page_size=PAGE_SIZES[name], max_tokens=max_tokens)
+    was = eng.ops.pp_prefill_min_ctas
+    eng.ops.pp_prefill_min_ctas = 0
+    try:
+        got = replay.run_steps(eng, steps)
+        eng.ops.check_errors()
+    finally:
+        eng.ops.pp_prefill_min_ctas = was
+    replay.compare(got, ref, ATOL["bfloat16"](scale), f"two-tile {name}/{mode}", RMS["bfloat16"](scale))
+    assert all(f == eng.num_pages for f in eng.cache.free_pages())
+
+
 def test_cut_independence_bfloat16(models):
     """In bfloat16 the bits of a cached key depend on the product that made it: a step of few
     tokens sums the projection in float32 and rounds once, after the rotation; a larger step takes
