@@ -221,7 +221,8 @@ __global__ void rope_store_kernel(T* __restrict__ qkv, const int* __restrict__ p
     }
 }
 
-// The bfloat16 case for many tokens (prompt portions): four tokens per CTA, 16-byte accesses.
+// The bfloat16 case for many tokens: four tokens per CTA (one, while that still leaves fewer
+// CTAs than four per SM: steps of a few dozen decode tokens), 16-byte accesses.
 // A work item is 8 consecutive dims of one head: a rotated pair of 8-dim groups (i, i + rot/2)
 // of a query or key head, 8 unrotated key dims, or 8 value dims.  Needs rot/2, hd - rot and hd
 // to be multiples of 8 and 16-byte aligned rows.
@@ -247,13 +248,13 @@ __global__ void __launch_bounds__(256)
 rope_store_bf16x8_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
                          const float* __restrict__ inv_freq, int T, int nq, int nkv, int hd, int rot,
                          const int* __restrict__ slot_map, __nv_bfloat16* __restrict__ kcache,
-                         __nv_bfloat16* __restrict__ vcache, int page_size) {
+                         __nv_bfloat16* __restrict__ vcache, int page_size, int toks_per_cta) {
     extern __shared__ float cs[];                 // per token: cos[rot/2], sin[rot/2]
     __shared__ int slot_s[kRopeToks];
     pdl_launch_dependents();
     // before the wait: positions and slots [descriptor], frequencies [constant]
-    const int t0 = blockIdx.x * kRopeToks;
-    const int n_tok = min(kRopeToks, T - t0);
+    const int t0 = blockIdx.x * toks_per_cta;
+    const int n_tok = min(toks_per_cta, T - t0);
     const int half = rot >> 1;
     for (int idx = threadIdx.x; idx < n_tok * half; idx += blockDim.x) {
         const int tt = idx / half, i = idx - tt * half;
@@ -548,7 +549,11 @@ SOMI_API int somi_add_rmsnorm(float* residual, const void* delta, int delta_dtyp
     // distributed shared memory, was slower: its two cluster barriers cost more than they saved.)
     // Many rows: fewer threads per row, more rows per SM.
     int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
-    if (n_out <= 32 && (H & 3) == 0) threads = min(1024, ((H / 4 + 31) / 32) * 32);
+    // (rows that add up split-K partial sums read `splits` times as much: they keep the one-pass
+    // form while there is at most a CTA per SM or two, so that every load of a row is in flight
+    // at once)
+    if ((n_out <= 32 || (delta_splits > 1 && n_out <= 256)) && (H & 3) == 0)
+        threads = min(1024, ((H / 4 + 31) / 32) * 32);
 #define SOMI_LAUNCH_NORM(TD, TO)                                                                 \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
@@ -576,10 +581,11 @@ SOMI_API int somi_rope_store(void* qkv, int dtype, const int* positions, const f
     const auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (dtype == SOMI_BF16 && T > 32 && rot > 0 && (rot & 15) == 0 && ((hd - rot) & 7) == 0 &&
         (hd & 7) == 0 && aligned16(qkv) && aligned16(kcache) && aligned16(vcache)) {
-        launch_pdl(rope_store_bf16x8_kernel, dim3((T + kRopeToks - 1) / kRopeToks), dim3(256),
-                   smem * kRopeToks, stream, static_cast<__nv_bfloat16*>(qkv), positions, inv_freq, T,
+        const int toks = T <= 4 * 148 ? 1 : kRopeToks;
+        launch_pdl(rope_store_bf16x8_kernel, dim3((T + toks - 1) / toks), dim3(256),
+                   smem * toks, stream, static_cast<__nv_bfloat16*>(qkv), positions, inv_freq, T,
                    nq, nkv, hd, rot, slot_map, static_cast<__nv_bfloat16*>(kcache),
-                   static_cast<__nv_bfloat16*>(vcache), page_size);
+                   static_cast<__nv_bfloat16*>(vcache), page_size, toks);
         return launch_status();
     }
     if (dtype == SOMI_F32)
