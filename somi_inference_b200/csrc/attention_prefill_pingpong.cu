@@ -13,14 +13,26 @@
 // so that while warp group A works on tile t's scores the tensor core runs B's products of
 // tile t-1 and B's scores of tile t, and the other way round.  The pipe executes in issue order,
 // which is what makes the aliasing of P over S safe: S_X(t+1) is issued after PV_X(t).
+// (Two issuing threads, one per query tile, fall into step with each other: both softmax warp
+// groups then want the exponential unit at the same time and a round takes a third longer.)
+// What the issuing thread does between products costs a hundred cycles and more apiece (a
+// barrier test, a fence, a commit), during which the pipe runs dry, so it does as little of
+// it as possible: it tests only the two p_full barriers in a round (the softmax warp group that
+// announces P has seen the value tile and the next key tile arrive, before it waits for the
+// scores, where it has time), it commits o_done only after a query tile's last key tile (the
+// commit behind s_full covers the output products issued before it), and it hands both stages
+// back at the end of a round.
 // An accumulator is rescaled in tensor memory only when its row maximum grows by more than 2^8
 // (probabilities up to 256 are harmless in float32 sums and bfloat16 operands).  Because tile B's
 // rows come later in the sequence, tile A runs out of key tiles first and writes its output
-// while B goes on.  Softmax is float32, base 2.  Every wait on an mbarrier is bounded and failure
-// is recorded in an error word.
+// while B goes on.  Softmax is float32, base 2; scaling, subtraction and the row sum work on
+// pairs of keys (`fma.rn.f32x2`, `add.rn.f32x2`), the maximum on three values at a time.  Every
+// wait on an mbarrier is bounded and failure is recorded in an error word.
 //
-// Warp roles: warps 0-3 softmax of tile A, 4-7 softmax of tile B, warp 8 key (and Q) producer,
-// warp 9 MMA issuer and owner of tensor memory, warp 10 value producer, warp 11 idle.
+// Warp roles: warps 0-3 softmax of tile A, 4-7 softmax of tile B (both clear the value stages
+// first), warp 8 key (and Q) producer, warp 9 MMA issuer and owner of tensor memory, warp 10
+// value producer, warp 11 idle.  Two key stages and three value stages at head size 128 (a value
+// tile is read a round later than the key tile that came with it), four and four at 64.
 //
 // The reference's prefill kernel (somi_inference/core/flash_attention_triton.py:31-194) is a
 // FlashAttention-2 loop on `tl.dot`; formulas in somi_inference/models/qwen2.py:158-186.
@@ -33,7 +45,10 @@ constexpr int kPpRows = 2 * kPpBM;       // rows of a CTA
 constexpr int kPpBN = 128;               // keys per tile
 constexpr int kPpThreads = 384;
 constexpr int kPpMaxStages = 4;
-__host__ __device__ constexpr int pp_stages(int hd) { return hd == 128 ? 2 : 4; }
+// A value tile is read one key tile later than the key tile that arrived with it (its products
+// wait for the softmax in between), so at the same distance of prefetch it needs a stage more.
+__host__ __device__ constexpr int pp_k_stages(int hd) { return hd == 128 ? 2 : 4; }
+__host__ __device__ constexpr int pp_v_stages(int hd) { return hd == 128 ? 3 : 4; }
 constexpr int kPpQHalf = kPpBM * 128;    // bytes of one [128 rows][64 elements] swizzled block
 constexpr int kPpKvHalf = kPpBN * 128;
 
@@ -51,16 +66,16 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
     constexpr int HALVES = HD / 64;
     constexpr int QTILE = HALVES * kPpQHalf;
     constexpr int TILE = HALVES * kPpKvHalf;
-    constexpr int STAGES = pp_stages(HD);
+    constexpr int KST = pp_k_stages(HD), VST = pp_v_stages(HD);
     constexpr uint32_t TmemCols = 512;                   // S_A | S_B | O_A | O_B, 128 columns each
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     unsigned char* Qs = base;                            // two query tiles
-    unsigned char* Ks = Qs + 2 * QTILE;                  // STAGES tiles
-    unsigned char* Vs = Ks + STAGES * TILE;              // STAGES tiles
+    unsigned char* Ks = Qs + 2 * QTILE;                  // KST tiles
+    unsigned char* Vs = Ks + KST * TILE;                 // VST tiles
     __shared__ __align__(8) unsigned long long q_full[2], k_full[kPpMaxStages], k_empty[kPpMaxStages],
-        v_full[kPpMaxStages], v_empty[kPpMaxStages], s_full[2], p_full[2], o_done[2];
+        v_full[kPpMaxStages], v_empty[kPpMaxStages], s_full[2], p_full[2], o_done[2], v_zeroed;
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
 
@@ -73,12 +88,13 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
             mbar_init(smem_u32(&p_full[x]), 4);          // one arrival per warp of the group
             mbar_init(smem_u32(&o_done[x]), 1);
         }
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < kPpMaxStages; ++s) {
             mbar_init(smem_u32(&k_full[s]), 1);
             mbar_init(smem_u32(&k_empty[s]), 1);
             mbar_init(smem_u32(&v_full[s]), 1);
             mbar_init(smem_u32(&v_empty[s]), 1);
         }
+        mbar_init(smem_u32(&v_zeroed), 8);               // one arrival per softmax warp
         mbar_fence_init();
         failed_s = 0;
     }
@@ -89,10 +105,6 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
-    // value rows that no copy fills (pages outside the request's range) must be finite numbers
-    for (int c = tid; c < STAGES * TILE / 16; c += kPpThreads)
-        reinterpret_cast<uint4*>(Vs)[c] = make_uint4(0, 0, 0, 0);
-    fence_proxy_async();
     t5::fence_before();
     __syncthreads();
     t5::fence_after();
@@ -117,7 +129,11 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
     const int* bt = block_table + static_cast<size_t>(req) * bt_stride;
 
     // The softmax threads hold a row of 128 scores in registers; the producer and issuing warps
-    // need few.  Warps 8-11 give registers back and the softmax warp groups take them.
+    // need few.  Warps 8-11 give registers back and the softmax warp groups take them.  The
+    // pool is what the CTA was given at launch, 12 warps x 168 registers a thread: 8 x 216 +
+    // 4 x 72 uses exactly that.  `setmaxnreg.inc` waits, without a limit, until the pool has what
+    // it asks for, so the two figures must never add up to more.
+    static_assert(8 * 216 + 4 * 72 <= 12 * 168, "setmaxnreg would wait for registers that never come");
     if (warp >= 8) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 72;\n");
       if (warp == 8 || warp == 10) {
@@ -134,8 +150,12 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
         }
         const int pages_per_tile = kPpBN / page_size;
         const int which = warp == 8 ? 0 : 1;
+        const int n_st = which ? VST : KST;
+        // no value copy before the softmax warps have cleared the value stages
+        if (which && !mbar_wait(smem_u32(&v_zeroed), 0)) failed_s = 1;
+        __syncwarp();
         for (int t = 0; t < n_t; ++t) {
-            const int st = t % STAGES;
+            const int st = t % n_st;
             const int kb = kb0 + t * kPpBN;
             const int p_lo = max(kb, kv_first) / page_size;
             const int p_hi = (min(kb + kPpBN, end_all) - 1) / page_size;
@@ -145,7 +165,7 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
             const uint32_t bar = smem_u32(which ? &v_full[st] : &k_full[st]);
             int ok = 1;
             if (lane == 0) {
-                ok = mbar_wait(smem_u32(which ? &v_empty[st] : &k_empty[st]), ((t / STAGES) & 1) ^ 1) ? 1 : 0;
+                ok = mbar_wait(smem_u32(which ? &v_empty[st] : &k_empty[st]), ((t / n_st) & 1) ^ 1) ? 1 : 0;
                 if (ok) mbar_expect_tx(bar, static_cast<uint32_t>(p_hi - p_lo + 1) * page_size * HD * 2);
                 else failed_s = 1;
             }
@@ -178,8 +198,18 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
                 if (ok && !mbar_wait(smem_u32(bar), parity)) ok = false;
                 t5::fence_after();
             };
+            // the same with the test that returns at once: this thread has nothing else to do,
+            // and wakes up sooner than from the test that may suspend it
+            auto spin = [&](unsigned long long* bar, int parity) {
+                if (ok) {
+                    int i = 0;
+                    while (!mbar_test_now(smem_u32(bar), parity))
+                        if (++i > 8000000) { ok = false; break; }
+                }
+                t5::fence_after();
+            };
             auto scores = [&](int x, int t) {            // S_x(t) = Q_x K(t)^T
-                const uint64_t kd = k_desc + (((t % STAGES) * TILE) >> 4);
+                const uint64_t kd = k_desc + (((t % KST) * TILE) >> 4);
                 const uint64_t qd = q_desc + ((x * QTILE) >> 4);
 #pragma unroll
                 for (int k16 = 0; k16 < HD / 16; ++k16)
@@ -190,12 +220,14 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
                 t5::commit(smem_u32(&s_full[x]));
             };
             auto outputs = [&](int x, int t) {           // O_x += P_x(t) V(t)
-                const uint64_t vd = v_desc + (((t % STAGES) * TILE) >> 4);
+                const uint64_t vd = v_desc + (((t % VST) * TILE) >> 4);
 #pragma unroll
                 for (int k16 = 0; k16 < kPpBN / 16; ++k16)
                     t5::mma_ts(tmem_o + x * kPpBN, tmem_s + x * kPpBN + 8 * k16,
                                vd + ((k16 * 16 * 128) >> 4), idesc_pv, (t > 0 || k16 > 0) ? 1u : 0u);
-                t5::commit(smem_u32(&o_done[x]));
+                // A commit covers every product issued so far: s_full of tile t + 1 also says
+                // that O holds tile t, so o_done is only needed after a query tile's last.
+                if (t + 1 == (x == 0 ? n_a : n_t)) t5::commit(smem_u32(&o_done[x]));
             };
             wait(&q_full[0], 0);
             wait(&k_full[0], 0);
@@ -206,34 +238,41 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
             }
             if (ok) t5::commit(smem_u32(&k_empty[0]));
             for (int t = 0; t < n_t && ok; ++t) {
-                const int st = t % STAGES;
-                // the tiles this iteration reads arrived long ago: their barriers are tested
-                // before the wait for the probabilities, so that no test (a couple of hundred
-                // cycles even on a completed barrier) sits between the products of a query tile
-                wait(&v_full[st], (t / STAGES) & 1);
-                if (t + 1 < n_t) wait(&k_full[(t + 1) % STAGES], ((t + 1) / STAGES) & 1);
+                // The key and value tiles these products read have been seen by the softmax
+                // warp group that announces P (it waits for them before it arrives), so this
+                // thread tests nothing but the two p_full barriers in an iteration: every test
+                // and every commit is time in which this thread issues no product.
                 if (t < n_a) {
-                    wait(&p_full[0], t & 1);
+                    spin(&p_full[0], t & 1);
                     if (!ok) break;
                     outputs(0, t);
                     if (t + 1 < n_a) scores(0, t + 1);
                 }
                 if (has_b) {
-                    wait(&p_full[1], t & 1);
+                    spin(&p_full[1], t & 1);
                     if (!ok) break;
                     outputs(1, t);
+                    if (t + 1 < n_t) scores(1, t + 1);
                 }
-                t5::commit(smem_u32(&v_empty[st]));
-                if (t + 1 < n_t) {
-                    if (has_b) scores(1, t + 1);
-                    t5::commit(smem_u32(&k_empty[(t + 1) % STAGES]));
-                }
+                // both stages are handed back at the end, so that no commit sits between the
+                // products of a query tile
+                t5::commit(smem_u32(&v_empty[t % VST]));
+                if (t + 1 < n_t) t5::commit(smem_u32(&k_empty[(t + 1) % KST]));
             }
             if (!ok) failed_s = 1;       // the softmax warps run out of their bounded waits
         }
       }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 216;\n");
+        // Value rows that no copy fills (pages outside the request's range) must be finite
+        // numbers, whatever the shared memory held before.  These warps have nothing to do
+        // until the first scores are there, so they clear the value stages while the keys and
+        // queries are on their way; the value producer waits for them.
+        for (int c = tid; c < VST * TILE / 16; c += 8 * 32)
+            reinterpret_cast<uint4*>(Vs)[c] = make_uint4(0, 0, 0, 0);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&v_zeroed));
         // ---- softmax: warp group x serves query tile x, one thread per row
         const int x = warp >> 2;
         if (x == 0 || has_b) {
@@ -252,6 +291,17 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
             float m = -INFINITY, l = 0.f;        // m: the reference maximum in use (log2 units)
             bool ok = true;
             for (int t = 0; t < n_x; ++t) {
+                // On behalf of the issuing thread: the values of this tile and the keys of the
+                // next have arrived before this warp group announces P(t).  They are tested
+                // here, where the warp would wait for the scores anyway (a test costs a few
+                // hundred cycles even on a completed barrier), by the whole warp, so that it
+                // stays converged for the aligned instructions.
+                if (q == 0) {
+                    ok = mbar_wait(smem_u32(&v_full[t % VST]), (t / VST) & 1, ok ? 400000 : 1) && ok;
+                    if (t + 1 < n_x)
+                        ok = mbar_wait(smem_u32(&k_full[(t + 1) % KST]), ((t + 1) / KST) & 1,
+                                       ok ? 400000 : 1) && ok;
+                }
                 ok = mbar_wait(smem_u32(&s_full[x]), t & 1, ok ? 400000 : 1) && ok;
                 t5::fence_after();
                 const int kb = kb0 + t * kPpBN;
@@ -265,7 +315,8 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
                 float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
                 if (tile_inner) {
 #pragma unroll
-                    for (int j = 0; j < 128; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(sv[j]));
+                    for (int j = 0; j < 128; j += 2)
+                        mx[(j >> 1) & 3] = fmax3(mx[(j >> 1) & 3], __uint_as_float(sv[j]), __uint_as_float(sv[j + 1]));
                 } else {
 #pragma unroll
                     for (int j = 0; j < 128; ++j) {
@@ -289,9 +340,8 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
                     rescale = true;
                 }
                 if (__any_sync(0xffffffffu, rescale)) {
-                    // O of the tiles so far must be complete before it is rescaled in tensor memory
-                    if (t >= 1) ok = mbar_wait(smem_u32(&o_done[x]), (t - 1) & 1, ok ? 400000 : 1) && ok;
-                    t5::fence_after();
+                    // O holds the tiles so far: the commit behind s_full covered the products
+                    // of tile t - 1 as well (issued before S(t) by the same thread)
 #pragma unroll
                     for (int c = 0; c < HD / 32; ++c) {
                         uint32_t ov[32];
@@ -307,30 +357,37 @@ paged_prefill_pp_kernel(const __grid_constant__ CUtensorMap q_map,
                 const float neg_m = m == -INFINITY ? 0.f : -m;
                 // ---- probabilities, written over the scores as bfloat16 pairs: chunk c's 32 keys
                 // become 16 columns at 16 c (every score is in registers by now)
-                float ps[4] = {0.f, 0.f, 0.f, 0.f};
+                // (scaling, subtraction and the row sum on pairs of keys: one instruction for two)
+                const uint64_t scale2 = pair_f32(scale_log2e, scale_log2e), neg_m2 = pair_f32(neg_m, neg_m);
+                uint64_t ps2[2] = {pair_f32(0.f, 0.f), pair_f32(0.f, 0.f)};
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     uint32_t pk[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + 2 * j]), scale_log2e, neg_m));
-                        const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + 2 * j + 1]), scale_log2e, neg_m));
-                        ps[(2 * j) & 3] += p0;
-                        ps[(2 * j + 1) & 3] += p1;
+                        float a0, a1;
+                        unpair_f32(fma_f32x2(pair_f32(__uint_as_float(sv[c * 32 + 2 * j]),
+                                                      __uint_as_float(sv[c * 32 + 2 * j + 1])),
+                                             scale2, neg_m2), a0, a1);
+                        const float p0 = fast_exp2(a0), p1 = fast_exp2(a1);
+                        ps2[j & 1] = add_f32x2(ps2[j & 1], pair_f32(p0, p1));
                         pk[j] = pack_bf16(p0, p1);
                     }
                     t5::st16(s_addr + c * 16, pk);
                 }
-                ps[0] += ps[2];
-                ps[1] += ps[3];
-                l += ps[0] + ps[1];
+                {
+                    float s0, s1, s2, s3;
+                    unpair_f32(ps2[0], s0, s1);
+                    unpair_f32(ps2[1], s2, s3);
+                    l += (s0 + s2) + (s1 + s3);
+                }
                 t5::wait_st();
                 t5::fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&p_full[x]));
             }
             // ---- the output of this row
-            ok = mbar_wait(smem_u32(&o_done[x]), (n_x - 1) & 1, ok ? 400000 : 1) && ok;
+            ok = mbar_wait(smem_u32(&o_done[x]), 0, ok ? 400000 : 1) && ok;
             t5::fence_after();
             if (!ok) failed_s = 1;
             const float inv = 1.0f / l;
@@ -370,7 +427,8 @@ int launch_prefill_pp(const CUtensorMap* q_map, const CUtensorMap* kv_map, long 
                       long long v_row0, const int* block_table, int bt_stride, const int* cu_q,
                       const int* ctx_len, const int* tiles, int n_tiles, int nq, int nkv,
                       int page_size, float scale, int window, void* out, cudaStream_t stream) {
-    const size_t smem = 2 * (HD / 64) * kPpQHalf + 2 * pp_stages(HD) * (HD / 64) * kPpKvHalf + 1024;
+    const size_t smem = 2 * (HD / 64) * kPpQHalf +
+                        (pp_k_stages(HD) + pp_v_stages(HD)) * (HD / 64) * kPpKvHalf + 1024;
     cudaFuncSetAttribute(paged_prefill_pp_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          (int)smem);
     dim3 grid(static_cast<unsigned>(nq) * n_tiles);

@@ -36,6 +36,19 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same test without the hardware's grace period: returns at once.  For a thread that has
+// other barriers to look at meanwhile.
+__device__ __forceinline__ bool mbar_test_now(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: true when the phase completed, false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = 400000) {
     for (int i = 0; i < limit; ++i)
