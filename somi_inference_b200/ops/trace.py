@@ -7,9 +7,11 @@ floating-point operations it has to do; while a `LaunchTrace` is active an event
 after each of them, and the time of a launch is the distance to the event before it.  Without
 an active trace `note` costs one comparison.
 
-Times taken this way are those of an eager step (no CUDA graph): launches are far enough
-apart on the host for short kernels to be measured with the gaps between them, so shares and
-rooflines of the long kernels are what the table is for.
+Times taken this way are those of an eager step (no CUDA graph, no overlap of a kernel's start
+with its predecessor's end).  The host needs longer to issue a short kernel than the GPU to run
+it, so the trace first puts a spinning kernel of a few milliseconds on the stream: the host
+issues the step's launches behind it, and when it ends they run back to back with nothing but
+the events between them.
 """
 
 from __future__ import annotations
@@ -30,14 +32,17 @@ def note(label: str, nbytes: float = 0.0, flops: float = 0.0, detail: str = "") 
 
 
 class LaunchTrace:
-    def __init__(self) -> None:
+    def __init__(self, head_start_ms: float = 8.0) -> None:
         self._events: list[torch.cuda.Event] = []
         self._rows: list[tuple[str, float, float, str]] = []
+        self._head_start_cycles = int(head_start_ms * 1e-3 * 1.9e9)
 
     def __enter__(self) -> "LaunchTrace":
         global _active
         if _active is not None:
             raise RuntimeError("a launch trace is already active")
+        if self._head_start_cycles > 0:
+            torch.cuda._sleep(self._head_start_cycles)       # a bounded spin, then the step
         ev = torch.cuda.Event(enable_timing=True)
         ev.record()
         self._events.append(ev)
