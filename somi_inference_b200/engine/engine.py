@@ -219,6 +219,10 @@ class Engine:
             # only writes the cache slots of its own tokens, with the same values.
             before = self.ops.launches
             graph = torch.cuda.CUDAGraph()
+            if len(self._graphs) == 0:
+                # the shared memory pool lives only as long as a graph uses it: after every
+                # graph has gone (the descriptor moved) this capture starts a new one
+                self._graph_pool = None
             with torch.no_grad(), torch.cuda.graph(graph, pool=self._graph_pool):
                 static_logits = self.model.forward(batch, self.cache)
             if self._graph_pool is None:

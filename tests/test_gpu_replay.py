@@ -176,3 +176,28 @@ def test_steps_replayed_from_graphs_match_plain(models, name, dtype):
     assert graphs.hits >= 12, f"only {graphs.hits} steps were replayed"
     eng.ops.check_errors()
     replay.compare(got, ref, ATOL[dtype](scale), f"graphs {name}/{dtype}", RMS[dtype](scale))
+
+
+def test_graphs_are_captured_anew_after_the_descriptor_buffer_moved(models):
+    """When a step needs a larger descriptor buffer than the engine holds, the buffer is
+    allocated anew and every captured graph is void.  The next layouts are captured again
+    (in a memory pool of their own: the old one went with its last graph) and their steps give
+    the plain logits like any other."""
+    from somi_inference_b200.engine import Engine, StepEntry
+    d, cfg, reqs, ref, scale = models[("A", torch.bfloat16)]
+    rid = list(reqs)[1]
+    toks = reqs[rid]
+    eng = Engine(d, dtype="bfloat16", page_size=PAGE_SIZES["A"], max_tokens=256)
+    got = {}
+    logits = eng.step([StepEntry("x", toks[:8], [7])]).float().cpu()
+    got[(rid, 7)] = logits[0]
+    for i in range(8, 40):
+        got[(rid, i)] = eng.step([StepEntry("x", [toks[i]], [0])]).float().cpu()[0]
+    assert len(eng._graphs) >= 1 and eng._graphs.hits >= 20
+    captures = eng._graphs.captures
+    eng.builder._alloc(2 * eng.builder._capacity)          # what a step beyond the capacity does
+    for i in range(40, len(toks)):
+        got[(rid, i)] = eng.step([StepEntry("x", [toks[i]], [0])]).float().cpu()[0]
+    assert eng._graphs.captures > captures, "no layout was captured after the buffer moved"
+    eng.ops.check_errors()
+    replay.compare(got, ref, ATOL["bfloat16"](scale), "graphs after a moved descriptor", RMS["bfloat16"](scale))
