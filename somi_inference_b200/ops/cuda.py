@@ -431,12 +431,16 @@ class CudaOps:
     GEMM_BF16, GEMM_F32, GEMM_PARTIAL_F32, GEMM_SWIGLU = 0, 1, 2, 3
 
     def skinny_splits(self, M: int, N: int, K: int) -> int:
-        """How many ranges of K to run side by side: enough CTAs for about two per SM, at least
-        four K blocks each, and partial sums (4 * splits * M * N bytes, written and read back)
-        that stay below a quarter of the weight's own bytes."""
+        """How many ranges of K to run side by side: CTAs for about one and a half per SM, at
+        least three K blocks each, at most eight (the consumer reads every partial sum: 4 *
+        splits * M * N bytes, written and read back), and partial sums that stay below a quarter
+        of the weight's own bytes.  Measured with the consumer (norm or rotary kernel) behind
+        each product in CUDA graphs, 1 and 8 tokens: more splits than this cost the 0.5B shape's
+        down projection 1.2 µs (16 -> 8) and the 7B shape's output projection 0.4 µs (10 -> 8);
+        past two CTAs per SM a product takes a third longer."""
         tiles = -(-N // 128)
         k_blocks = -(-K // 64)
-        return max(1, min(296 // tiles, k_blocks // 4, K // (16 * M), 16))
+        return max(1, min(224 // tiles, k_blocks // 3, K // (16 * M), 8))
 
     def skinny_supported(self, M: int, N: int, K: int, dtype) -> bool:
         """Whether the tensor-memory kernel takes x[M, K] @ w[N, K]^T (few tokens, bfloat16)."""
