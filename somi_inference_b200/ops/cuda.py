@@ -447,10 +447,12 @@ class CudaOps:
         if not (self.use_skinny_gemm and dtype == torch.bfloat16
                 and 1 <= M <= self.skinny_max_tokens and K % 8 == 0 and N >= 1):
             return False
-        # measured (CUDA graphs of back-to-back products, and whole decode steps at batch 32 and
-        # 64): above 16 tokens this kernel wins only where a CTA streams a long K range of a
-        # large matrix; short K (few stages per CTA) and small matrices go to the library
-        return M <= 16 or (K >= 2048 and N * K >= (32 << 20))
+        # measured (CUDA graphs of back-to-back products with their consumers, and whole decode
+        # steps at batch 32 and 64): above 16 tokens this kernel wins only where a CTA streams a
+        # long K range, of a large matrix or of one that is several times as long as it is wide
+        # (the 0.5B shape's down projection at 24-64 tokens: 7.8-9.5 µs against the library's
+        # 11.4-11.7); short K (few stages per CTA) and small matrices go to the library
+        return M <= 16 or (K >= 2048 and (N * K >= (32 << 20) or K >= 4 * N))
 
     def _gemm_map(self, t: torch.Tensor, box_rows: int) -> int:
         key = (t.data_ptr(), t.shape[0], t.shape[1], box_rows)
