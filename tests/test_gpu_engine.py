@@ -162,6 +162,63 @@ def test_preemption_on_the_gpu_gives_the_same_tokens(root):
     assert [r.output_tokens for r in reqs] == want
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2])
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_serving_with_random_arrivals_few_pages_and_aborts(root, name, seed):
+    """A serving run made by a random number generator: requests of random lengths arrive at
+    random steps and want random numbers of tokens, the page pool is small enough for
+    preemptions, and some requests are taken out half way.  Every request that was left alone
+    must have produced exactly the greedy tokens of the plain implementation, an aborted one
+    a prefix of them, and no page may be lost.  (float32, so that the largest logit is the
+    same on both sides.)"""
+    import random
+    from somi_inference_b200 import LLM, SamplingParams
+    from somi_inference_b200.engine.scheduler import RequestStatus
+    d = make_model(name, root, torch.float32, std=STD)
+    cfg, w = plain.load_folder(d)
+    rng = random.Random(1000 + seed)
+    ps = PAGE_SIZES[name]
+    n_req = 10
+    lens = [rng.choice([1, 2, 3, 7, 17, 31, 45, 64, 80]) for _ in range(n_req)]
+    news = [rng.randint(1, 24) for _ in range(n_req)]
+    arrivals = sorted(rng.randint(0, 12) for _ in range(n_req))
+    # room for the largest request and a little more: requests are admitted while pages are
+    # free and preempted when the running ones outgrow the pool
+    pages = -(-(max(lens) + max(news)) // ps) + 3
+    llm = LLM(d, num_blocks=pages, block_size=ps, max_concurrent=4, dtype="float32",
+              chunk_size=rng.choice([8, 16, 32]), max_num_batched_tokens=rng.choice([24, 48, 96]))
+    prompts = [random_tokens(n, cfg["vocab_size"], 300 + 10 * seed + i) for i, n in enumerate(lens)]
+    reqs = [llm.make_request(p, max_new_tokens=k, sampling_params=SamplingParams(temperature=0.0),
+                             ignore_eos=True) for p, k in zip(prompts, news)]
+    abort_at = {i: rng.randint(1, max(1, news[i] - 1)) for i in rng.sample(range(n_req), 3)}
+    aborted = set()
+    pending = list(zip(arrivals, range(n_req)))
+    step = 0
+    while pending or llm.scheduler.has_unfinished():
+        while pending and pending[0][0] <= step:
+            llm.scheduler.add_request(reqs[pending.pop(0)[1]])
+        llm.step()
+        llm.scheduler.drain_finished()
+        for i, k in abort_at.items():
+            if (i not in aborted and len(reqs[i].output_tokens) >= k
+                    and reqs[i].status is not RequestStatus.FINISHED):
+                assert llm.abort(reqs[i])
+                aborted.add(i)
+        llm.engine.cache.check_consistency()
+        step += 1
+        assert step < 2000, "the serving loop does not come to an end"
+    for i, (p, r) in enumerate(zip(prompts, reqs)):
+        want = plain.greedy(cfg, w, p, news[i])
+        if i in aborted:
+            assert r.output_tokens == want[:len(r.output_tokens)] and len(r.output_tokens) >= 1
+        else:
+            assert r.output_tokens == want, f"request {i} (prompt of {lens[i]} tokens)"
+    assert llm.engine.cache.free_pages() == [pages] * len(llm.engine.cache.groups)
+    llm.engine.ops.check_errors()
+    assert sum(r.num_preemptions for r in reqs) > 0, "the pool was meant to be too small"
+    assert aborted, "some requests were meant to be taken out"
+
+
 @pytest.mark.parametrize("chunks", [2, 3])
 def test_decoding_with_several_chunks_per_cta(root, chunks):
     """Steps with thousands of 128-key chunks run decode attention with CTAs that walk through
