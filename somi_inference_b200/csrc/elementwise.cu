@@ -92,6 +92,56 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
     const TD* d = delta ? delta + row * H : nullptr;
     float ss = 0.f;
     TO* o = out + static_cast<size_t>(b) * H;
+    if ((H & 3) == 0 && splits == 1 && H <= static_cast<int>(blockDim.x) * 16) {
+        // Up to four vectors a thread and one delta: every load of the row is issued before the
+        // first result is needed (a loop would wait for each vector's round trip in turn).
+        F4 v[4];
+        const int step = blockDim.x * 4;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x * 4 + k * step;
+            if (i < H) v[k] = load4(r + i);
+        }
+        if (d) {
+            F4 dv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = threadIdx.x * 4 + k * step;
+                if (i < H) dv[k] = load4(d + i);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = threadIdx.x * 4 + k * step;
+                if (i < H) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) v[k].v[e] += dv[k].v[e];
+                    if (write_back) store4(r + i, v[k]);
+                }
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x * 4 + k * step;
+            if (i < H) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) ss += v[k].v[e] * v[k].v[e];
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float inv = 1.0f / sqrtf(ss / static_cast<float>(H) + eps);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int i = threadIdx.x * 4 + k * step;
+            if (i < H) {
+                const F4 w = k == 0 ? w_first : load4_any(weight, weight_dtype, i);
+                F4 y;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) y.v[e] = v[k].v[e] * inv * w.v[e];
+                store4(o + i, y);
+            }
+        }
+        return;
+    }
     if ((H & 3) == 0) {
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
             F4 v = load4(r + i);
