@@ -164,3 +164,28 @@ def test_random_orders_lose_nothing(seed):
     for r in list(live):
         m.release(r)
     assert m.free_pages() == [24, 24]
+
+
+def test_what_a_request_would_need_and_what_it_holds():
+    """The questions a scheduler may ask before it reserves: pages a request would need for more
+    tokens (per group, a windowed group counting only what its window keeps), who is live, and
+    how many table entries a slot uses."""
+    m = manager(num_pages=12, page_size=4, windows=(None, 6))
+    m.register("a")
+    assert m.live_requests() == ["a"]
+    assert m.pages_needed("a", 9) == [3, 3]
+    m.reserve("a", 9)
+    m.commit("a")
+    slot = m.slot("a")
+    assert m.blocks_in_use(0, slot) == 3 and m.blocks_in_use(1, slot) == 3
+    # five more tokens: positions 9..13 need one more page of four (page 2 has room for 9..11)
+    assert m.pages_needed("a", 5)[0] == 1
+    m.reserve("a", 5)
+    m.commit("a")
+    # the windowed group has given back the pages that positions 14 - 6 + 1 = 9.. no longer read
+    assert len(m.held_pages("a", 1)) < len(m.held_pages("a", 0)) == 4
+    m.register("b")
+    assert sorted(m.live_requests()) == ["a", "b"]
+    m.release("a")
+    assert m.live_requests() == ["b"]
+    m.check_consistency()

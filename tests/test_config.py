@@ -19,6 +19,12 @@ def test_reads_every_size_from_the_file():
     assert c.max_position_embeddings == 256
 
 
+def test_from_a_file_or_a_folder(tmp_path):
+    (tmp_path / "config.json").write_text(json.dumps(TINY_B))
+    assert Qwen2Config.from_json(str(tmp_path)) == Qwen2Config.from_json(str(tmp_path / "config.json"))
+    assert Qwen2Config.from_json(str(tmp_path)).vocab_size == 1000
+
+
 def test_head_dim_explicit_wins_over_quotient():
     assert Qwen2Config.from_dict(TINY_C).head_dim == 32       # 80 / 6 is not even an integer
     assert Qwen2Config.from_dict(TINY_A).head_dim == 16
