@@ -80,6 +80,39 @@ def test_generation_through_the_entry_point_matches_plain_greedy(root):
     assert llm.generate(prompts[1], max_new_tokens=4, temperature=0.0) == outs[1][:4]
 
 
+def test_text_in_text_out_through_a_tokenizer_in_the_model_folder(root):
+    """`LLM.generate` with a string: the prompt goes through the tokenizer that lies in the model
+    folder and the new tokens come back as text (somi_inference/entrypoints/llm.py:118-160).  The
+    tokenizer here is a word-level one written by the test (one word per id); a folder without a
+    tokenizer refuses text with a clear error."""
+    import json
+    import os
+    import shutil
+    tokenizers = pytest.importorskip("tokenizers")
+    pytest.importorskip("transformers")
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import Whitespace
+    src = make_model("A", root, torch.float32, std=0.08)
+    cfg, w = plain.load_folder(src)
+    bare = LLM(src, num_blocks=16, block_size=8, max_concurrent=1, device="cpu", dtype="float32",
+               ops=HostOps())
+    with pytest.raises(ValueError, match="no tokenizer"):
+        bare.generate("w5 w17", max_new_tokens=2, temperature=0.0)
+    d = os.path.join(root, "A_with_tokenizer")
+    shutil.copytree(src, d)
+    vocab = {f"w{i}": i for i in range(cfg["vocab_size"])}
+    tok = tokenizers.Tokenizer(WordLevel(vocab, unk_token="w0"))
+    tok.pre_tokenizer = Whitespace()
+    tok.save(os.path.join(d, "tokenizer.json"))
+    with open(os.path.join(d, "tokenizer_config.json"), "w") as f:
+        json.dump({"tokenizer_class": "PreTrainedTokenizerFast", "unk_token": "w0"}, f)
+    llm = LLM(d, num_blocks=16, block_size=8, max_concurrent=1, device="cpu", dtype="float32",
+              ops=HostOps())
+    ids = [5, 17, 3, 200, 41]
+    text = llm.generate(" ".join(f"w{i}" for i in ids), max_new_tokens=5, temperature=0.0, ignore_eos=True)
+    assert text == " ".join(f"w{i}" for i in plain.greedy(cfg, w, ids, 5))
+
+
 def test_sampled_generation_matches_the_plain_sampler(root):
     """Tiny B at temperature 0.7 with top-k, top-p and a repetition penalty, portions of 32 mixed
     with decoding: every token is the one the plain pipeline draws with the same (seed, counter)."""
